@@ -196,11 +196,31 @@ int b2_batch_set_row(b2_model* m, b2_kv* kv, int slot, int active, const b2_samp
  *                      cached); softmax with a per-head sink term in the denominator; per-head sigmoid output gate
  *   B2_MIXER_HGRN2     gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T silu(W_q h), with the forget gate
  *                      f = l + (1 - l) sigmoid(W_f h + b) bounded below by a learned l; per-head unit-RMS norm
+ *                      Options (zero = the form above): la_q_rank > 0 sends the queries through a latent of their own
+ *                      (q = W_uq rms_w(W_dq h)); la_rot_dim > 0 adds a rotated part to every query head and ONE rotated key
+ *                      part per token, shared by all heads and cached beside c (rotation rot_*); la_no_sink / la_no_gate drop
+ *                      the sink term / the head gates; la_kv_from >= 0: the layer has no W_dkv and reads the cache rows of
+ *                      that earlier layer with its own W_uk / W_uv; mask_* limits the visible keys
+ *   B2_MIXER_GQA_ATTN  attention with grouped key/value heads: q, k, v (and a per-channel sigmoid output gate) from one input,
+ *                      a short causal depthwise convolution over time on q, k and v, rotary positions on q and k (rot_*),
+ *                      optionally values rotated by their own position over all of vdim and the head's output turned back by
+ *                      the query's position (ga_rot_values), ga_sink != 0: one extra term exp(ga_sink_value) in the softmax
+ *                      denominator; mask_* limits the visible keys
+ * Visible keys (mask_kind): B2_MASK_CAUSAL all j <= i; B2_MASK_WINDOW 0 <= i - j < mask_size; B2_MASK_CHUNK j <= i with
+ * floor(i / mask_size) == floor(j / mask_size), chunks counted from position 0 of the sequence.
+ * Rotation (rot_*): pairs (2m, 2m+1), m < rot_dims / 2, of a head turn by p * f_m, f_m = rot_base^(-2m / rot_dims); with
+ * rot_factor > 0 the frequencies are blended towards f_m / rot_factor over the pairs whose wavelength lies between
+ * rot_original / rot_fast and rot_original / rot_slow turns (YaRN) and cos / sin carry the factor 0.1 ln(rot_factor) + 1.
  * Blocks: B2_BLOCK_POST_LN adds the LayerNorm of every sublayer's OUTPUT; B2_BLOCK_PRE_RMS1 is pre-norm,
- * x += residual_mult * sublayer(g * unit_rms(x)) with ONE learned number g per norm (also in front of the head).
+ * x += residual_mult * sublayer(g * unit_rms(x)) with ONE learned number g per norm (also in front of the head);
+ * B2_BLOCK_SANDWICH_RMS norms both sides with weighted RMS norms, x += rms_w'(sublayer(u + conv(u))), u = rms_w(x), where
+ * conv is a causal depthwise convolution over time of input_conv_taps taps (0: none) whose last taps - 1 inputs are carried
+ * per slot, for the mixer and for the feed-forward of every layer.
  * Feed-forwards: B2_FF_RELU_SQ (W_down relu(W_up x)^2), B2_FF_POLYNORM (biased projections around
- * a N(z) + b N(z^2) + c N(z^3) + e, N = division by the token's root mean square), B2_FF_MOE (sigmoid router, group-limited
- * top-k, SiLU-gated experts without biases, optional shared expert).
+ * a N(z) + b N(z^2) + c N(z^3) + e, N = division by the token's root mean square), B2_FF_MOE (router, group-limited
+ * top-k, experts without biases, optional shared expert; moe_score: sigmoid or softmax scores; moe_group_score: a group counts
+ * by its two best experts or by its best; moe_raw_weights: the chosen scores are the weights as they are, else divided by their
+ * sum and scaled; moe_act: SiLU-gated experts or W_down relu(W_up x)^2).
  * A model may add a hashed bigram row to every token embedding, loop a block of layers several times with the same tensors
  * (every pass has its own cache/state; before a pass the embedding output is added again from the second pass on, and a
  * learned per-pass vector always), and soft-cap its logits with tanh.
@@ -210,9 +230,13 @@ int b2_batch_set_row(b2_model* m, b2_kv* kv, int slot, int active, const b2_samp
  * compute: B2_COMPUTE_BF16 = bf16 x bf16 -> fp32 matrix products on bf16 weights, everything else fp32;
  *          B2_COMPUTE_F32  = true fp32 throughout (weights widened at load, FMA products, no TF32). */
 enum { B2_ARCH_LLAVA = 0, B2_ARCH_LAYER_LIST = 1 };
-enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2, B2_MIXER_LATENT_ATTN = 3, B2_MIXER_HGRN2 = 4 };
+enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2, B2_MIXER_LATENT_ATTN = 3, B2_MIXER_HGRN2 = 4, B2_MIXER_GQA_ATTN = 5 };
 enum { B2_FF_RELU_SQ = 0, B2_FF_POLYNORM = 1, B2_FF_MOE = 2 };
-enum { B2_BLOCK_POST_LN = 0, B2_BLOCK_PRE_RMS1 = 1 };
+enum { B2_BLOCK_POST_LN = 0, B2_BLOCK_PRE_RMS1 = 1, B2_BLOCK_SANDWICH_RMS = 2 };
+enum { B2_MASK_CAUSAL = 0, B2_MASK_WINDOW = 1, B2_MASK_CHUNK = 2 };
+enum { B2_MOE_SCORE_SIGMOID = 0, B2_MOE_SCORE_SOFTMAX = 1 };
+enum { B2_MOE_GROUP_TOP2_SUM = 0, B2_MOE_GROUP_MAX = 1 };
+enum { B2_MOE_ACT_SWIGLU = 0, B2_MOE_ACT_RELU_SQ = 1 };
 enum { B2_COMPUTE_BF16 = 0, B2_COMPUTE_F32 = 1 };
 typedef struct b2_seq_layer_desc {
     int32_t type;            /* B2_MIXER_* */
@@ -236,6 +260,19 @@ typedef struct b2_seq_layer_desc {
     float la_scale;
     /* B2_MIXER_HGRN2 */
     int32_t g_heads, g_dim, g_vdim;
+    /* B2_FF_MOE, further forms (zero: sigmoid scores, groups by their two best, normalised weights, SiLU-gated experts) */
+    int32_t moe_score, moe_group_score, moe_raw_weights, moe_act;   /* B2_MOE_* */
+    /* B2_MIXER_LATENT_ATTN, further forms (zero: direct queries, no rotated part, per-head sink and gate, own cache rows) */
+    int32_t la_q_rank, la_rot_dim, la_no_sink, la_no_gate;
+    int32_t la_kv_from;      /* 1 + the earlier layer whose cache rows this layer reads; 0: its own */
+    /* B2_MIXER_GQA_ATTN */
+    int32_t ga_heads, ga_kv_heads, ga_dim, ga_vdim, ga_conv;   /* ga_conv: taps of the convolution on q, k, v (<= 1: none) */
+    int32_t ga_rot_values, ga_sink;
+    float ga_scale, ga_sink_value;
+    /* visible keys and rotation of the attention mixers above */
+    int32_t mask_kind, mask_size;   /* B2_MASK_* */
+    int32_t rot_dims;               /* rotated leading dimensions of a head (of the rotated part, for latent attention); even */
+    float rot_base, rot_factor, rot_original, rot_fast, rot_slow;   /* rot_factor 0: plain frequencies */
 } b2_seq_layer_desc;
 typedef struct b2_seq_model_desc {
     int32_t width, vocab, n_layers;
@@ -249,6 +286,8 @@ typedef struct b2_seq_model_desc {
     int32_t bigram_buckets, bigram_mul_prev, bigram_mul_cur;  /* hashed bigram embedding: row (prev * mul_prev + cur * mul_cur) mod
                                                                  buckets, row `buckets` for a sequence's first token; 0 buckets = none */
     int32_t loop_start, loop_stop, loop_times;                /* layers [start, stop) run `times` times in a row; times 0: no loop */
+    float logit_scale;       /* factor on the logits; 0 = 1 */
+    int32_t input_conv_taps; /* B2_BLOCK_SANDWICH_RMS: taps of the convolution every sublayer's input passes (<= 1: none) */
 } b2_seq_model_desc;
 int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* layers, b2_model** out);
 /* Layer RUNS of one forward pass (a looped layer counts every time): rows of b2_append_tokens' resid_out; -1 for other models */
@@ -258,7 +297,10 @@ int b2_seq_model_runs(const b2_model* m);
  * r,k,v,g,w1,w2,w0,u,norm,o}, l<i>.mlp.{up,down}; Linear weights are [out, in].
  * B2_BLOCK_PRE_RMS1 models: embed, bigram, loop.step, head, final.norm, l<i>.norm1, l<i>.norm2 (one number each),
  * l<i>.mix.{q,dkv,dkv.norm,uk,uv,sink,g,o} (latent attention), l<i>.mix.{q,f,f.b,lower,v,norm,o} (HGRN2),
- * l<i>.mlp.{up,up.b,down,down.b,act} (PolyNorm), l<i>.mlp.{router,e<j>.gate,e<j>.up,e<j>.down,shared.gate,shared.up,shared.down}. */
+ * l<i>.mlp.{up,up.b,down,down.b,act} (PolyNorm), l<i>.mlp.{router,e<j>.gate,e<j>.up,e<j>.down,shared.gate,shared.up,shared.down}.
+ * B2_BLOCK_SANDWICH_RMS models: embed, head, final.norm, l<i>.{norm1,norm1b,norm2,norm2b} (width each), l<i>.{canon1,canon2}
+ * ([width, taps]), l<i>.mix.{dq,dq.norm,uq,dkv,dkv.norm,uk,uv,o} (latent attention; no dkv* with la_kv_from),
+ * l<i>.mix.{q,k,v,q.conv,k.conv,v.conv,g,o} (grouped attention), l<i>.mlp.{router,e<j>.up,e<j>.down,shared.up,shared.down}. */
 /* Feed the next n tokens of the request in cache slot `slot` (a portion of its prompt, or all of it): the slot's state and
  * key/value rows continue from its current length, or from an empty sequence when restart != 0 (whatever the slot held
  * is then dead: nothing needs clearing). want_host lists n_want indices into these n tokens whose logits are written to

@@ -15,7 +15,7 @@ OBJ = os.path.join(HERE, "build")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libb2llava.so")
 SOURCES = ["gemm_tcgen05.cu", "gemm_2cta.cu", "gemm_skinny.cu", "quant_fp8.cu", "gemv.cu", "decode_mega.cu", "attention.cu", "attention_tc.cu", "norms.cu", "vit_ops.cu", "misc_ops.cu", "sampling.cu", "preprocess.cu", "model.cu",
-           "linear_generic.cu", "norms_f32.cu", "recurrent.cu", "attention_bias.cu", "moe.cu", "seq_engine.cu"]
+           "linear_generic.cu", "norms_f32.cu", "rotary.cu", "recurrent.cu", "attention_bias.cu", "moe.cu", "seq_engine.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",

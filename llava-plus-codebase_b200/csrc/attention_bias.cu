@@ -7,7 +7,9 @@
 // to its slot's cache, which attn_prepare has already extended by the rows of this call.
 // The same kernels serve attention over a shared latent (one cached row per token that is key AND value of every head:
 // kcache == vcache, dk == dv <= 512, G = 1), without bias table or soft-cap (rel == null), and with a per-head sink: one
-// extra term exp(sink[h]) in the softmax denominator that has no key and no value.
+// extra term exp(sink[h]) in the softmax denominator that has no key and no value (or exp(sink_value) for every head). A cached
+// row may be longer than the value it holds (dv < dk: a latent followed by a rotated key part). The visible keys of a row may be
+// limited to a sliding window or to the row's chunk of positions: keys in front of the first visible one are never loaded.
 #include <math.h>
 
 #include "common.cuh"
@@ -20,6 +22,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+// first position a row at position pos sees
+__device__ __forceinline__ int mask_first(int pos, int kind, int size) {
+    if (kind == MASK_WINDOW) return max(0, pos - size + 1);
+    if (kind == MASK_CHUNK) return pos / size * size;
+    return 0;
 }
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -75,11 +83,12 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
     for (int d = lane; d < a.dk; d += 32) q[d] = a.q[(size_t)r * a.ldq + (size_t)h * a.dk + d];
     __syncwarp();
     const float* K = a.kcache + ((size_t)slot * a.G + g) * a.Smax * a.dk;
-    const float* V = a.vcache + ((size_t)slot * a.G + g) * a.Smax * a.dv;
-    int lo = 0, hi = pos + 1;
+    const size_t vrs = a.vcache == a.kcache ? (size_t)a.dk : (size_t)a.dv;   // keys that hold the value: the key row's pitch
+    const float* V = a.vcache + ((size_t)slot * a.G + g) * a.Smax * vrs;
+    int lo = mask_first(pos, a.mask_kind, a.mask_size), hi = pos + 1;
     if (a.nsplit > 1) {
-        const int per = ((pos + a.nsplit) / a.nsplit + 31) / 32 * 32;
-        lo = sp * per;
+        const int per = ((hi - lo + a.nsplit - 1) / a.nsplit + 31) / 32 * 32;
+        lo += sp * per;
         hi = min(pos + 1, lo + per);
     }
     float m = -INFINITY, l = 0.f, o[AT_MAXC];
@@ -115,7 +124,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
         for (int c = 0; c < AT_MAXC; ++c) o[c] *= corr;
         for (int jj = 0; jj < nk; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const float* vr = V + (size_t)(j0 + jj) * a.dv;
+            const float* vr = V + (size_t)(j0 + jj) * vrs;
 #pragma unroll
             for (int c = 0; c < AT_MAXC; ++c) {
                 const int d = lane + 32 * c;
@@ -133,8 +142,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
         }
     } else {
         float inv = 1.f / l;
-        if (a.sink != nullptr) {   // the sink joins the denominator once, under the common maximum
-            const float sk = a.sink[h], mf = fmaxf(m, sk), c0 = expf(m - mf);
+        if (a.sink != nullptr || a.sink_fixed) {   // the sink joins the denominator once, under the common maximum
+            const float sk = a.sink != nullptr ? a.sink[h] : a.sink_value, mf = fmaxf(m, sk), c0 = expf(m - mf);
             inv = c0 / fmaf(l, c0, expf(sk - mf));
         }
 #pragma unroll
@@ -193,8 +202,12 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
     const float* sVal = shared_kv ? sK : sV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int slot = a.row_slot[r0];
-    int maxpos = -1;
-    for (int i = 0; i < nrows; ++i) maxpos = max(maxpos, a.row_pos[r0 + i]);
+    int maxpos = -1, first = 0x7fffffff;   // last and first key position any row of the tile sees
+    for (int i = 0; i < nrows; ++i) {
+        const int p = a.row_pos[r0 + i];
+        maxpos = max(maxpos, p);
+        if (p >= 0) first = min(first, mask_first(p, a.mask_kind, a.mask_size));
+    }
     if (maxpos < 0) return;
     if (VEC && a.ldq % 4 == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0) {
         // a row's heads of this chunk are consecutive in q: HG * dk floats per row, copied 16 bytes at a time
@@ -206,10 +219,10 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
             sQ[e] = a.q[(size_t)(r0 + p / HG) * a.ldq + (size_t)(h0 + p % HG) * dk + d];
         }
     }
-    int lo = 0, hi = maxpos + 1;
+    int lo = first, hi = maxpos + 1;
     if (a.nsplit > 1) {
-        const int per = ((maxpos + a.nsplit) / a.nsplit + TL_KT - 1) / TL_KT * TL_KT;
-        lo = sp * per;
+        const int per = ((hi - lo + a.nsplit - 1) / a.nsplit + TL_KT - 1) / TL_KT * TL_KT;
+        lo += sp * per;
         hi = min(maxpos + 1, lo + per);
     }
     // cache slabs [slot][head][position][size], or (kv_row_stride > 0) one matrix [position][head * size] made for this call
@@ -219,12 +232,13 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
     const float* V = mat ? a.vcache + (size_t)g * dv : a.vcache + ((size_t)slot * a.G + g) * a.Smax * dv;
     const bool vecv = VEC && dv % 4 == 0 && vrs % 4 == 0 && (reinterpret_cast<uintptr_t>(V) & 15) == 0;   // 16-byte value rows
     float m[TL_PPW], l[TL_PPW], o[TL_PPW][MAXC];
-    int ppos[TL_PPW];
+    int ppos[TL_PPW], pfirst[TL_PPW];
 #pragma unroll
     for (int i = 0; i < TL_PPW; ++i) {
         m[i] = -INFINITY; l[i] = 0.f;
         const int p = warp + TL_WARPS * i;
         ppos[i] = p < P ? a.row_pos[r0 + p / HG] : -1;
+        pfirst[i] = mask_first(max(ppos[i], 0), a.mask_kind, a.mask_size);
 #pragma unroll
         for (int c = 0; c < MAXC; ++c) o[i][c] = 0.f;
     }
@@ -253,7 +267,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
                     const float4 kv = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
                     for (int i = 0; i < TL_PPW; ++i) {
-                        if (ppos[i] >= j0) {           // idle pairs and pairs whose keys all lie ahead skip (warp-uniform)
+                        if (ppos[i] >= j0 && pfirst[i] < j0 + nk) {   // idle pairs and pairs whose keys all lie ahead or behind skip (warp-uniform)
                             const float4 qv = *reinterpret_cast<const float4*>(sQ + (warp + TL_WARPS * i) * dk + d);
                             sc[i] = fmaf(qv.x, kv.x, sc[i]); sc[i] = fmaf(qv.y, kv.y, sc[i]);
                             sc[i] = fmaf(qv.z, kv.z, sc[i]); sc[i] = fmaf(qv.w, kv.w, sc[i]);
@@ -265,7 +279,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
                     const float kv = kr[d];
 #pragma unroll
                     for (int i = 0; i < TL_PPW; ++i)
-                        if (ppos[i] >= j0) sc[i] = fmaf(sQ[(warp + TL_WARPS * i) * dk + d], kv, sc[i]);
+                        if (ppos[i] >= j0 && pfirst[i] < j0 + nk) sc[i] = fmaf(sQ[(warp + TL_WARPS * i) * dk + d], kv, sc[i]);
                 }
             }
         }
@@ -275,11 +289,11 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
         for (int i = 0; i < TL_PPW; ++i) {
             pr[i] = 0.f;
             const int pos = ppos[i];
-            if (pos < j0) continue;
+            if (pos < j0 || pfirst[i] >= j0 + nk) continue;   // no key of this tile is visible: the running maximum stays as it is
             any = true;
             const int head = h0 + (warp + TL_WARPS * i) % HG;
             const int j = j0 + lane;
-            const bool valid = lane < nk && j <= pos;
+            const bool valid = lane < nk && j <= pos && j >= pfirst[i];
             float sv = -INFINITY;
             if (valid) {
                 sv = sc[i] * a.scale;
@@ -327,8 +341,8 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
             }
         } else {
             float inv = 1.f / l[i];
-            if (a.sink != nullptr) {
-                const float sk = a.sink[head], mf = fmaxf(m[i], sk), c0 = expf(m[i] - mf);
+            if (a.sink != nullptr || a.sink_fixed) {
+                const float sk = a.sink != nullptr ? a.sink[head] : a.sink_value, mf = fmaxf(m[i], sk), c0 = expf(m[i] - mf);
                 inv = c0 / fmaf(l[i], c0, expf(sk - mf));
             }
 #pragma unroll
@@ -356,9 +370,10 @@ __global__ void __launch_bounds__(512) attn_merge_kernel(BiasAttnArgs a) {
         for (int s = lane; s < a.nsplit; s += 32)
             if (part[(size_t)s * stride + 1] > 0.f) mx = fmaxf(mx, part[(size_t)s * stride]);
         mx = warp_max(mx);
-        const float sk = a.sink != nullptr ? a.sink[h] : -INFINITY;
+        const bool has_sink = a.sink != nullptr || a.sink_fixed;
+        const float sk = a.sink != nullptr ? a.sink[h] : (a.sink_fixed ? a.sink_value : -INFINITY);
         mx = fmaxf(mx, sk);
-        float lsum = (a.sink != nullptr && lane == 0) ? expf(sk - mx) : 0.f;
+        float lsum = (has_sink && lane == 0) ? expf(sk - mx) : 0.f;
         for (int s = lane; s < a.nsplit; s += 32) {
             const float* ps = part + (size_t)s * stride;
             const float ws = ps[1] > 0.f ? expf(ps[0] - mx) : 0.f;
@@ -388,7 +403,8 @@ int check_args(const BiasAttnArgs& a, const char* who) {
     B2_CHECK_ARG(a.q && a.kcache && a.vcache && a.row_slot && a.row_pos && a.rows > 0, "%s: null argument", who);
     B2_CHECK_ARG(a.H > 0 && a.G > 0 && a.H % a.G == 0, "%s: %d query heads cannot share %d key/value heads", who, a.H, a.G);
     B2_CHECK_ARG(a.dk > 0 && a.dk <= 512 && a.dv > 0 && a.dv <= 512, "%s: head sizes %d / %d exceed 512", who, a.dk, a.dv);
-    B2_CHECK_ARG(a.vcache != a.kcache || a.dk == a.dv, "%s: keys that are also the values need dk == dv", who);
+    B2_CHECK_ARG(a.vcache != a.kcache || a.dv <= a.dk, "%s: keys that also hold the values need dv <= dk", who);
+    B2_CHECK_ARG(a.mask_kind == MASK_CAUSAL || ((a.mask_kind == MASK_WINDOW || a.mask_kind == MASK_CHUNK) && a.mask_size >= 1), "%s: mask %d of size %d", who, a.mask_kind, a.mask_size);
     B2_CHECK_ARG(a.kv_row_stride == 0 || (a.kv_row_stride_v > 0 && a.tile_rows >= 1 && a.vcache != a.kcache), "%s: key/value matrices need both pitches and the tiled kernel", who);
     return 0;
 }

@@ -312,12 +312,15 @@ int linear_batched_rows_f32(const float* A, int64_t lda, int64_t a_bs, const voi
 enum { GROUPED_TILE_ROWS = 64 };
 
 // ---- mixture of experts (moe.cu) ------------------------------------------------------------------------------------------
-// Router: scores s = sigmoid(logits); experts form `groups` equal groups of neighbours, a group's score is the sum of its two
-// largest scores, only experts of the best `keep` groups compete; the `top` largest are chosen (ties: the lower index);
-// w = s / (sum of the chosen s + 1e-20) * scale. idx / w: [rows, top].
+// Router: scores s = sigmoid(logits) (score_fn MOE_SCORE_SOFTMAX: softmax over the experts); experts form `groups` equal groups of
+// neighbours, a group's score is the sum of its two largest scores (group_score MOE_GROUP_MAX: its largest), only experts of
+// the best `keep` groups compete; the `top` largest are chosen (ties: the lower index); w = s / (sum of the chosen s + 1e-20) *
+// scale (raw_weights: w = s). idx / w: [rows, top].
+enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1, MOE_GROUP_TOP2_SUM = 0, MOE_GROUP_MAX = 1 };   // the values of B2_MOE_*
 struct MoeRouteArgs {
     const float* logits = nullptr; int64_t ld = 0;
     int rows = 0, experts = 0, top = 0, groups = 1, keep = 1;
+    int score_fn = 0, group_score = 0, raw_weights = 0;
     float scale = 1.f;
     int32_t* idx = nullptr; float* w = nullptr;
 };
@@ -379,6 +382,37 @@ int embed_rows_f32(const int32_t* tokens, const void* table, int table_dtype, fl
 // out[r, c] = a[r, c] * sigmoid(g[r, c])
 int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, float* out, int64_t ldo, int rows, int cols, cudaStream_t stream);
 
+// out[i] = x[row_index[i]] / sqrt(mean(x^2) + eps) * w (row_index null: row i; rows of pitch ld_in / ld_out); accumulate: out[i] += ...
+// (a normed sublayer output joining the residual stream)
+int rms_weight_f32(const float* in, int64_t ld_in, const int32_t* row_index, const float* w, float* out, int64_t ld_out, int accumulate, int rows,
+                   int cols, float eps, cudaStream_t stream);
+
+// ---- rotary positions (rotary.cu) -------------------------------------------------------------------------------------------
+// Pairs (2m, 2m+1), m < dims / 2, turn by position * f_m, f_m = base^(-2m / dims). factor > 0: f_m is blended towards f_m / factor
+// over the pairs between lo = max(floor(dim(fast)), 0) and hi = min(ceil(dim(slow)), dims - 1), dim(t) = dims ln(original / (2 pi t)) /
+// (2 ln base), and cos / sin are scaled by 0.1 ln(factor) + 1.
+struct RotaryDesc { int dims = 0; float base = 10000.f, factor = 0.f, original = 0.f, fast = 0.f, slow = 0.f; };
+// table_dev[p][m] = (cos, sin)(p * f_m) * scale for p < positions; computed on the host in double precision
+int rotary_table_build(const RotaryDesc& d, int positions, float2* table_dev);
+// For every live row r (position row_pos[r] >= 0) and head h < heads: the head's `size` entries at in[r * ld_in + h * hs_in] are copied
+// to out[r * ld_out + h * hs_out] (or to cache[slot][h][position][size]); the `pairs` pairs from entry `offset` on are turned by the
+// row's position (inverse: by minus the position); gate (nullable, [rows, ldg], entry h * size + d): the result times its sigmoid.
+// in == out is allowed.
+struct RotateArgs {
+    const float* in = nullptr; int64_t ld_in = 0; int hs_in = 0;
+    float* out = nullptr; int64_t ld_out = 0; int hs_out = 0;
+    float* cache = nullptr; int Smax = 0;
+    const float* gate = nullptr; int64_t ldg = 0;
+    const float2* table = nullptr;               // [positions][pairs]
+    int heads = 0, size = 0, offset = 0, pairs = 0, inverse = 0, rows = 0;
+    const int32_t* row_slot = nullptr; const int32_t* row_pos = nullptr;
+};
+int rotate_rows_f32(const RotateArgs& a, cudaStream_t stream);
+// Row of a low-rank key/value cache with a rotated key part: cache[slot][pos] = [unit_rms(in[r, :rank]) * gamma | the 2 * pairs entries
+// behind them turned by the row's position]; rows of the cache have rank + 2 * pairs entries
+int latent_rot_append_f32(const float* in, int64_t ld_in, const float* gamma, float* cache, const int32_t* row_slot, const int32_t* row_pos, int rows,
+                          int rank, int pairs, const float2* table, int Smax, float eps, cudaStream_t stream);
+
 // ---- recurrent mixers (recurrent.cu) ----------------------------------------------------------------------------------
 // Causal depthwise convolution + SiLU with a carried tail: out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]);
 // inputs before the start of the call come from tail[slot][taps-1][C] (zeros when the segment starts a sequence); the tail is
@@ -386,6 +420,11 @@ int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, f
 // max_n: the longest segment of the call (the launch grid covers that many rows per segment).
 int causal_conv_silu_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C,
                          int taps, const SeqSeg* segs, int nseg, int max_n, cudaStream_t stream);
+// The same convolution in its other forms: bias nullable; flags CONV_SILU (the activation above), CONV_ADD_INPUT (out = in + conv(in):
+// a sublayer input that passes a convolution beside itself). in and out are different buffers.
+enum { CONV_SILU = 1, CONV_ADD_INPUT = 2 };
+int causal_conv_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C, int taps,
+                    int flags, const SeqSeg* segs, int nseg, int max_n, cudaStream_t stream);
 // Token shift: out[s][t, c] = x[t, c] + (x[t-1, c] - x[t, c]) * mu[s][c] for s < n_mix, with x[-1] = prev[slot] (zeros at a sequence
 // start); prev[slot] := the segment's last row. out is [n_mix][rows_total][cols].
 int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out, int64_t out_stride, int cols, int n_mix, const SeqSeg* segs,
@@ -412,12 +451,13 @@ struct ScanArgs {
 int linear_scan_f32(const ScanArgs& a, cudaStream_t stream);
 
 // ---- attention with unit-RMS q/k, query temperature, tanh soft-cap and a bucketed distance bias (attention_bias.cu) -----
+enum { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_CHUNK = 2 };
 struct BiasAttnArgs {
     float* q = nullptr; int64_t ldq = 0;          // [rows, H*dk]: normalised and scaled in place by attn_prepare
     const float* k = nullptr; int64_t ldk = 0;    // [rows, G*dk] projections of this call's rows
     const float* v = nullptr; int64_t ldv = 0;    // [rows, G*dv]
-    float* kcache = nullptr; float* vcache = nullptr;  // [slots][G][Smax][dk] / [..][dv] fp32; the same pointer (dk == dv): a cached row
-                                                       // is key and value at once
+    float* kcache = nullptr; float* vcache = nullptr;  // [slots][G][Smax][dk] / [..][dv] fp32; the same pointer (dv <= dk): a cached row
+                                                       // is the key and, with its first dv entries, the value
     float* out = nullptr; int64_t ldo = 0;        // [rows, H*dv]
     const float* rel = nullptr;                   // [buckets, H] learned bias; null: no bias
     const int32_t* bucket_of = nullptr;           // [Smax]: bias row of a distance (built on the host)
@@ -428,6 +468,9 @@ struct BiasAttnArgs {
     int64_t kv_row_stride = 0, kv_row_stride_v = 0;  // > 0: kcache / vcache are matrices [position][G * dk] / [position][G * dv] of the call's
                                                   // one slot (keys and values made for this call) with these pitches, not cache slabs
     const float* sink = nullptr;                  // [H] or null: exp(sink[h]) joins the softmax denominator (no key, no value)
+    int sink_fixed = 0; float sink_value = 0.f;   // sink_fixed (with sink null): exp(sink_value) does, for every head
+    int mask_kind = 0, mask_size = 0;             // MASK_* (the values of B2_MASK_*): row at position i sees j <= i (causal), and only i - j < size (window) or
+                                                  // floor(i / size) == floor(j / size) (chunk)
     float* partial = nullptr; int nsplit = 1;     // split-KV scratch [rows*H*nsplit*(dv+2)] when nsplit > 1
     int tile_rows = 0;                            // consecutive rows that share a slot (a prompt portion: its rows; a decode step: 1);
                                                   // 0: one warp per (row, head) without shared key/value tiles

@@ -1,4 +1,4 @@
-// Mixture-of-experts feed-forward of the layer-list decoders: sigmoid router with group-limited top-k choice, the plan that
+// Mixture-of-experts feed-forward of the layer-list decoders: sigmoid or softmax router with group-limited top-k choice, the plan that
 // sorts (token, choice) pairs by expert into tiles of one expert each, the gated activation, and the weighted sum of the
 // chosen experts' outputs. The expert products themselves are grouped Linears (linear_generic.cu). Router scores, the choice
 // and the weights are fp32; the order of a pair inside its expert's tile does not change its result, and the sum over a
@@ -31,19 +31,35 @@ __global__ void moe_route_kernel(MoeRouteArgs a) {
     float* s = sm + (size_t)warp * (2 * E + G);
     float* gs = s + E;
     float* taken = gs + G;
-    for (int e = lane; e < E; e += 32) {
-        s[e] = 1.f / (1.f + expf(-a.logits[(size_t)r * a.ld + e]));
-        taken[e] = 0.f;
+    if (a.score_fn == MOE_SCORE_SOFTMAX) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, a.logits[(size_t)r * a.ld + e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float den = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float v = expf(a.logits[(size_t)r * a.ld + e] - mx);
+            s[e] = v;
+            den += v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        for (int e = lane; e < E; e += 32) { s[e] /= den; taken[e] = 0.f; }
+    } else {
+        for (int e = lane; e < E; e += 32) {
+            s[e] = 1.f / (1.f + expf(-a.logits[(size_t)r * a.ld + e]));
+            taken[e] = 0.f;
+        }
     }
     __syncwarp();
-    // a group's score: the sum of its two largest scores (of its one score, when a group is a single expert)
+    // a group's score: the sum of its two largest scores (of its one score, when a group is a single expert), or its largest
     for (int g = lane; g < G; g += 32) {
         float b1 = -INFINITY, b2v = -INFINITY;
         for (int e = g * per; e < (g + 1) * per; ++e) {
             const float v = s[e];
             if (v > b1) { b2v = b1; b1 = v; } else if (v > b2v) { b2v = v; }
         }
-        gs[g] = per > 1 ? b1 + b2v : b1;
+        gs[g] = (per > 1 && a.group_score != MOE_GROUP_MAX) ? b1 + b2v : b1;
     }
     __syncwarp();
     // keep the best groups: experts of the others are marked as taken. G - keep rounds remove the weakest group each
@@ -75,7 +91,7 @@ __global__ void moe_route_kernel(MoeRouteArgs a) {
     }
     if (lane < a.top) {
         a.idx[(size_t)r * a.top + lane] = mine_e;
-        a.w[(size_t)r * a.top + lane] = mine / (sum + 1e-20f) * a.scale;
+        a.w[(size_t)r * a.top + lane] = a.raw_weights ? mine : mine / (sum + 1e-20f) * a.scale;
     }
 }
 

@@ -1,7 +1,7 @@
 // fp32 normalisations and row helpers of the layer-list decoders: LayerNorm of a sublayer's output added to the residual
 // stream, gathered LayerNorm in front of the output head, grouped unit-RMS norm with a SiLU gate (before or after the
 // norm), embedding rows as fp32, the row map of a call; for pre-norm blocks: the one-number RMS norm (with the opening of a
-// looped pass folded in), PolyNorm, the logit soft-cap, per-head sigmoid gates, token + hashed-bigram embedding, and the
+// looped pass folded in), the weighted RMS norm (plain, gathered, or added onto the residual stream), PolyNorm, the logit soft-cap, per-head sigmoid gates, token + hashed-bigram embedding, and the
 // normalised latent row of a low-rank key/value cache. Statistics, sums and outputs are fp32 throughout; any width.
 #include "common.cuh"
 #include "kernels.h"
@@ -125,6 +125,22 @@ __global__ void rms_scalar_kernel(float* __restrict__ x, const int32_t* __restri
     if (out == nullptr) return;   // only the update of x was asked for
     const float mul = g[0] / sqrtf(block_sum(q, red) / (float)cols + eps);
     for (int c = threadIdx.x; c < cols; c += blockDim.x) out[r * cols + c] = xr[c] * mul;
+}
+
+// weighted RMS norm of a (gathered) row; accumulate: added onto out
+__global__ void rms_weight_kernel(const float* __restrict__ in, int64_t ld_in, const int32_t* __restrict__ row_index, const float* __restrict__ w,
+                                  float* __restrict__ out, int64_t ld_out, int accumulate, int cols, float eps) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const float* xr = in + (row_index != nullptr ? (size_t)row_index[r] : r) * ld_in;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) q = fmaf(xr[c], xr[c], q);
+    const float mul = 1.f / sqrtf(block_sum(q, red) / (float)cols + eps);
+    float* o = out + r * ld_out;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = xr[c] * mul * w[c];
+        o[c] = accumulate ? o[c] + v : v;
+    }
 }
 
 // dst[b][c][r] = src[b][r][c] for elements of 2 or 4 bytes
@@ -327,6 +343,14 @@ int rms_scalar_f32(float* x, const int32_t* row_index, const float* g, const flo
                    float eps, cudaStream_t st) {
     B2_CHECK_ARG(x && rows > 0 && cols > 0 && ((g && out) || (!out && (add || vec))), "rms_scalar: bad argument");
     rms_scalar_kernel<<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(x, row_index, g, add, vec, out, cols, eps);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int rms_weight_f32(const float* in, int64_t ld_in, const int32_t* row_index, const float* w, float* out, int64_t ld_out, int accumulate, int rows,
+                   int cols, float eps, cudaStream_t st) {
+    B2_CHECK_ARG(in && w && out && rows > 0 && cols > 0, "rms_weight: bad argument");
+    rms_weight_kernel<<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(in, ld_in, row_index, w, out, ld_out, accumulate, cols, eps);
     B2_LAUNCH_CHECK();
     return 0;
 }

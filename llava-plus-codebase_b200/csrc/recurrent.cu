@@ -19,10 +19,11 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 // call, or the carried tail for positions before the call) and walks the tile. The compute kernel only READS the tail; a
 // second small kernel replaces it afterwards, so tiles never race with the update.
 constexpr int CONV_MAX_TAPS = 16, CONV_TILE = 32;
-__global__ void __launch_bounds__(128) causal_conv_silu_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ w,
-                                                               const float* __restrict__ bias, const float* __restrict__ tail,
-                                                               float* __restrict__ out, int64_t ld_out, int C, int taps,
-                                                               const SeqSeg* __restrict__ segs) {
+template <int FLAGS>   // CONV_SILU | CONV_ADD_INPUT
+__global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ w,
+                                                          const float* __restrict__ bias, const float* __restrict__ tail,
+                                                          float* __restrict__ out, int64_t ld_out, int C, int taps,
+                                                          const SeqSeg* __restrict__ segs) {
     const SeqSeg sg = segs[blockIdx.z];
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int tt0 = blockIdx.y * CONV_TILE;
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(128) causal_conv_silu_kernel(const float* __re
         }
         win[jp] = v;
     }
-    const float b = bias[c];
+    const float b = bias != nullptr ? bias[c] : 0.f;
     float* op = out + (size_t)sg.row0 * ld_out + c;
     const int t_end = min(sg.n, tt0 + CONV_TILE);
     for (int t0 = tt0; t0 < t_end; t0 += 8) {
@@ -61,7 +62,8 @@ __global__ void __launch_bounds__(128) causal_conv_silu_kernel(const float* __re
                 float acc = b;
 #pragma unroll
                 for (int jp = 0; jp < CONV_MAX_TAPS; ++jp) acc = fmaf(wt[jp], win[jp], acc);
-                op[(size_t)(t0 + u) * ld_out] = silu_f(acc);
+                if (FLAGS & CONV_ADD_INPUT) acc += v[u];
+                op[(size_t)(t0 + u) * ld_out] = (FLAGS & CONV_SILU) ? silu_f(acc) : acc;
             }
         }
     }
@@ -284,11 +286,22 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
 
 int causal_conv_silu_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C,
                          int taps, const SeqSeg* segs, int nseg, int max_n, cudaStream_t st) {
-    B2_CHECK_ARG(in && w && bias && tail && out && segs && C > 0 && nseg > 0, "causal_conv: bad argument");
+    B2_CHECK_ARG(bias != nullptr, "causal_conv_silu: null bias");
+    return causal_conv_f32(in, ld_in, w, bias, tail, out, ld_out, C, taps, CONV_SILU, segs, nseg, max_n, st);
+}
+
+int causal_conv_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C, int taps,
+                    int flags, const SeqSeg* segs, int nseg, int max_n, cudaStream_t st) {
+    B2_CHECK_ARG(in && w && (tail || taps == 1) && out && in != out && segs && C > 0 && nseg > 0, "causal_conv: bad argument");
     B2_CHECK_ARG(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: 1..%d taps are supported (got %d)", CONV_MAX_TAPS, taps);
     // the grid covers the longest segment the call may hold; tiles past a segment's end return at once
-    causal_conv_silu_kernel<<<dim3((C + 127) / 128, (max_n + CONV_TILE - 1) / CONV_TILE, nseg), 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out,
-                                                                                                             C, taps, segs);
+    const dim3 grid((C + 127) / 128, (max_n + CONV_TILE - 1) / CONV_TILE, nseg);
+    switch (flags & (CONV_SILU | CONV_ADD_INPUT)) {
+        case 0: causal_conv_kernel<0><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
+        case CONV_SILU: causal_conv_kernel<CONV_SILU><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
+        case CONV_ADD_INPUT: causal_conv_kernel<CONV_ADD_INPUT><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
+        default: causal_conv_kernel<CONV_SILU | CONV_ADD_INPUT><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
+    }
     B2_LAUNCH_CHECK();
     if (taps > 1) {
         causal_conv_tail_kernel<<<dim3((C + 127) / 128, nseg), 128, 0, st>>>(in, ld_in, tail, C, taps, segs);

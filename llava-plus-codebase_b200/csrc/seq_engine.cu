@@ -24,7 +24,10 @@ struct SeqWeights {   // tensors of one layer that owns its weights
     DevBuf qdg_w, dkv_norm, uk_w, ukT, uv_w, sink;      // latent attention: [q | dkv | g] fused; W_uk as stored and per head transposed to [rank][dim]
     DevBuf qfv_w, f_b, lower, hnorm;                    // HGRN2: [q | f | v] fused
     DevBuf up_b, down_b, down_b16, act_coef;            // PolyNorm feed-forward (bias of the second product also as bf16: GEMM epilogue)
-    DevBuf router_w, egu_w, ed_w, sgu_w, sd_w;          // experts: [E][gate | up][width], [E][width][ff]; shared expert [gate | up], down
+    DevBuf router_w, egu_w, ed_w, sgu_w, sd_w;          // experts: [E][gate | up][width] (ungated: [E][up][width]), [E][width][ff]; shared expert likewise
+    DevBuf canon1, canon2;                              // sandwich block: taps of the input convolutions [width][taps]
+    DevBuf dq_norm, uq_w, ukx_w;                        // latent attention, further forms: norm of the queries' latent, W_uq, and W_uk widened per
+                                                        // head by an identity block that carries the rotated key part ([H (dim + rot)][rank + rot])
     std::map<std::string, int> got;
 };
 
@@ -38,8 +41,10 @@ struct SeqLayerInfo {
     int dproj_ld = 0, lproj_ld = 0;                   // row pitch of the projection outputs (multiples of 8: tensor-core epilogue)
     int pq = 0, pproj = 0, pproj_ld = 0;              // latent attention / HGRN2: width of q, of the fused projection, its pitch
     int pv = 0;                                       // heads * vdim of those mixers
+    int lqw = 0, lqw_ld = 0, lrow = 0;                // latent attention: heads * (dim + rot_dim) and its pitch, a cache row (rank + rot_dim)
 };
-struct SeqRun { int layer; int pass; };               // one layer run; pass >= 0: the run opens pass `pass` of the looped block
+struct SeqRun { int layer; int pass; int kv_run; };   // one layer run; pass >= 0: the run opens pass `pass` of the looped block; kv_run: the run
+                                                      // whose cache rows a borrowing latent-attention layer reads (-1: its own)
 
 struct SeqModel {
     b2_seq_model_desc d;
@@ -49,6 +54,7 @@ struct SeqModel {
     DevBuf embed, head, final_w, final_b;
     DevBuf bigram, loop_step;          // [buckets + 1, width] in the weight dtype; [times, width] fp32
     DevBuf x0;                         // the embedding output, kept for the passes of a looped block
+    DevBuf hin;                        // sandwich block: a sublayer's input after its convolution
     DevBuf qabs, olat;                 // latent attention: queries carried into the latent space, latent-space outputs [rows, heads*rank]
     DevBuf ffa;                        // activated feed-forward rows
     DevBuf rlogit, moe_idx, moe_w, moe_pos, moe_src, moe_tile, moe_h, moe_a, moe_y, moe_a16, zero_idx;   // router and grouped expert products
@@ -70,6 +76,8 @@ struct SeqLayerState {
     DevBuf wkv, prev;                  // RWKV: [slots][heads][dim][dim], [slots][width]
     DevBuf lat;                        // latent attention: [slots][Smax][rank]
     DevBuf gla;                        // HGRN2: [slots][heads][dim][vdim]
+    DevBuf canon1, canon2;             // sandwich block: the last taps-1 inputs of both sublayers [slots][taps-1][width]
+    DevBuf rot_tab, vrot_tab;          // rotation tables (cos, sin) [Smax][pairs] of the queries / keys and of the values
 };
 struct SeqState {
     std::vector<SeqLayerState> layer;  // one per layer RUN
@@ -196,6 +204,283 @@ int attn_nsplit(int rows, int G, int max_seq) {
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------------------------
+// mixers and feed-forwards of the pre-norm and sandwich blocks: they read h [R, width] and write alpha * (their output) to
+// `target` [R, width] (accumulate: onto what it holds)
+// ------------------------------------------------------------------------------------------------------------------
+static void mask_of(const b2_seq_layer_desc& d, BiasAttnArgs& aa) {
+    aa.mask_kind = d.mask_kind;
+    aa.mask_size = d.mask_size;
+}
+
+// Attention over a low-rank latent. S: the run's own state (rotation table); KS: the state whose cache rows it reads (its own,
+// or an earlier layer's). slot / ctx_end as for seq_forward.
+static int latent_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& W, SeqLayerState& S, SeqLayerState& KS, const float* h, float* target,
+                        float alpha, int accumulate, int R, int nseg, int slot, int ctx_end, cudaStream_t st) {
+    SeqModel& s = *m->seq;
+    SeqState& state = *kv->seq;
+    const b2_seq_layer_desc& d = L.d;
+    const Lin lin{m, st};
+    const int width = s.d.width;
+    const float eps = s.d.norm_eps;
+    const int H = d.la_heads, dk = d.la_dim, dv = d.la_vdim, rank = d.la_rank, rd = d.la_rot_dim, qh = dk + rd, lrow = L.lrow;
+    const int pairs = rd > 0 ? d.rot_dims / 2 : 0;
+    const bool own = d.la_kv_from == 0, gate = d.la_no_gate == 0;
+    const int max_n = nseg == 1 ? R : 1;
+    const int32_t* row_slot = s.row_slot.as<int32_t>();
+    const int32_t* row_pos = s.row_pos.as<int32_t>();
+    const float2* tab = S.rot_tab.as<float2>();
+    float* proj = s.proj.as<float>();  // [R, q (or the queries' latent) | dkv | g]
+    B2_TRY(lin(h, width, W.qdg_w, L.pproj, width, proj, L.pproj_ld, R));
+    float* q = proj;
+    int64_t ldq = L.pproj_ld;
+    if (d.la_q_rank > 0) {   // queries through their latent: norm in place, then up
+        B2_TRY(rms_weight_f32(proj, L.pproj_ld, nullptr, W.dq_norm.as<float>(), proj, L.pproj_ld, 0, R, d.la_q_rank, eps, st));
+        q = s.act.as<float>();
+        ldq = L.lqw_ld;
+        B2_TRY(lin(proj, L.pproj_ld, W.uq_w, L.lqw, d.la_q_rank, q, ldq, R));
+    }
+    if (own) B2_TRY(latent_rot_append_f32(proj + L.pq, L.pproj_ld, W.dkv_norm.as<float>(), S.lat.as<float>(), row_slot, row_pos, R, rank, pairs, tab,
+                                          kv->max_seq, eps, st));
+    const float* gates = gate ? proj + L.pq + (own ? lrow : 0) : nullptr;
+    float* lat_cache = KS.lat.as<float>();
+    BiasAttnArgs aa;
+    aa.sink = d.la_no_sink ? nullptr : W.sink.as<float>();
+    aa.H = H; aa.Smax = kv->max_seq; aa.rows = R;
+    aa.eps = eps; aa.scale = d.la_scale; aa.softcap = 0.f;
+    aa.row_slot = row_slot; aa.row_pos = row_pos;
+    aa.tile_rows = max_n;
+    aa.partial = state.attn_partial.as<float>();
+    mask_of(d, aa);
+    float* y = s.y.as<float>();
+    if (nseg == 1 && R >= latent_materialise_rows() && ctx_end > 0) {
+        // a long portion: per-head keys and values of every visible position of the slot so far are made from the cached rows
+        // with two products (the key product carries the rotated part through an identity block), and the attention runs over
+        // them with the heads' own sizes
+        if (pairs > 0) {
+            RotateArgs ra;
+            ra.in = q; ra.ld_in = ldq; ra.hs_in = qh; ra.out = q; ra.ld_out = ldq; ra.hs_out = qh;
+            ra.table = tab; ra.heads = H; ra.size = qh; ra.offset = dk; ra.pairs = pairs; ra.rows = R; ra.row_pos = row_pos;
+            B2_TRY(rotate_rows_f32(ra, st));
+        }
+        const float* lat = lat_cache + (size_t)slot * kv->max_seq * lrow;
+        const int first = d.mask_kind == B2_MASK_WINDOW ? std::max(0, ctx_end - R - d.mask_size + 1)
+                        : d.mask_kind == B2_MASK_CHUNK ? (ctx_end - R) / d.mask_size * d.mask_size : 0;
+        const DevBuf& wk = rd > 0 ? W.ukx_w : W.uk_w;
+        for (int m0 = first; m0 < ctx_end; m0 += s.rows) {
+            const int mc = std::min(s.rows, ctx_end - m0);
+            B2_TRY(lin(lat + (size_t)m0 * lrow, lrow, wk, L.lqw, lrow, state.kmat.as<float>() + (size_t)m0 * state.kmat_ld, state.kmat_ld, mc));
+            B2_TRY(lin(lat + (size_t)m0 * lrow, lrow, W.uv_w, L.pv, rank, state.vmat.as<float>() + (size_t)m0 * state.vmat_ld, state.vmat_ld, mc));
+        }
+        aa.q = q; aa.ldq = ldq;
+        aa.kcache = state.kmat.as<float>(); aa.vcache = state.vmat.as<float>();
+        aa.kv_row_stride = state.kmat_ld; aa.kv_row_stride_v = state.vmat_ld;
+        aa.out = y; aa.ldo = L.pv;
+        aa.G = H; aa.dk = qh; aa.dv = dv; aa.nsplit = 1;
+        B2_TRY(attn_bias_f32(aa, st));
+    } else {
+        // absorbed form: q_h -> W_uk_h^T q_h lives in the latent space (the rotated part rides behind it), so scores and values
+        // read the cached rows directly, and W_uv_h carries the latent-space output to the head's values
+        float* qabs = s.qabs.as<float>();
+        const int64_t lq = (int64_t)H * lrow, lo = (int64_t)H * rank;
+        const int round_a = s.d.compute == B2_COMPUTE_BF16;
+        if (R <= 8) {
+            B2_TRY(linear_batched_rows_f32(q, ldq, qh, W.ukT.p, (int64_t)rank * dk, s.w_dtype, qabs, lq, lrow, H, R, rank, dk, round_a, st));
+        } else {
+            for (int hh = 0; hh < H; ++hh)
+                B2_TRY(lin(q + (size_t)hh * qh, ldq, W.ukT, rank, dk, qabs + (size_t)hh * lrow, lq, R, LIN_NONE, 1.f, 0, nullptr, (size_t)hh * rank));
+        }
+        if (rd > 0) {
+            RotateArgs ra;
+            ra.in = q + dk; ra.ld_in = ldq; ra.hs_in = qh; ra.out = qabs + rank; ra.ld_out = lq; ra.hs_out = lrow;
+            ra.table = tab; ra.heads = H; ra.size = rd; ra.offset = 0; ra.pairs = pairs; ra.rows = R; ra.row_pos = row_pos;
+            B2_TRY(rotate_rows_f32(ra, st));
+        }
+        aa.q = qabs; aa.ldq = lq;
+        aa.kcache = lat_cache; aa.vcache = lat_cache;
+        aa.out = s.olat.as<float>(); aa.ldo = lo;
+        aa.G = 1; aa.dk = lrow; aa.dv = rank;
+        aa.nsplit = attn_nsplit(R, (H + 31) / 32, kv->max_seq);
+        if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
+        B2_TRY(attn_bias_f32(aa, st));
+        if (R <= 8) {   // with the heads' sigmoid gates in the same launch
+            y = s.gated.as<float>();
+            B2_TRY(linear_batched_rows_f32(s.olat.as<float>(), lo, rank, W.uv_w.p, (int64_t)dv * rank, s.w_dtype, y, L.pv, dv, H, R, dv, rank, round_a, st,
+                                           gates, L.pproj_ld));
+        } else {
+            for (int hh = 0; hh < H; ++hh)
+                B2_TRY(lin(s.olat.as<float>() + (size_t)hh * rank, lo, W.uv_w, dv, rank, y + (size_t)hh * dv, L.pv, R, LIN_NONE, 1.f, 0, nullptr, (size_t)hh * dv));
+        }
+    }
+    if (gate && y != s.gated.as<float>()) {
+        B2_TRY(head_gate_f32(y, L.pv, gates, L.pproj_ld, s.gated.as<float>(), L.pv, R, H, dv, st));
+        y = s.gated.as<float>();
+    }
+    return lin(y, L.pv, W.o_w, width, L.pv, target, width, R, LIN_NONE, alpha, accumulate);
+}
+
+// Attention with grouped key/value heads, a short convolution on q / k / v, rotary q / k, optionally rotated values, a masked
+// softmax with an optional fixed sink, and a per-channel sigmoid output gate.
+static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& W, SeqLayerState& S, const float* h, float* target, float alpha,
+                     int accumulate, int R, int nseg, cudaStream_t st) {
+    SeqModel& s = *m->seq;
+    SeqState& state = *kv->seq;
+    const b2_seq_layer_desc& d = L.d;
+    const Lin lin{m, st};
+    const int width = s.d.width;
+    const int H = d.ga_heads, G = d.ga_kv_heads, dk = d.ga_dim, dv = d.ga_vdim;
+    const int max_n = nseg == 1 ? R : 1;
+    const SeqSeg* segs = s.segs.as<SeqSeg>();
+    const int32_t* row_slot = s.row_slot.as<int32_t>();
+    const int32_t* row_pos = s.row_pos.as<int32_t>();
+    float* proj = s.proj.as<float>();  // [R, nq | nk | nv | ng]
+    B2_TRY(lin(h, width, W.lproj_w, L.lproj, width, proj, L.lproj_ld, R));
+    float* qkv = proj;
+    int64_t ldc = L.lproj_ld;
+    if (d.ga_conv > 1) {
+        qkv = s.act.as<float>();
+        ldc = L.conv_ch;
+        B2_TRY(causal_conv_f32(proj, L.lproj_ld, W.conv_w.as<float>(), nullptr, S.conv_tail.as<float>(), qkv, ldc, L.conv_ch, d.ga_conv, 0, segs, nseg, max_n, st));
+    }
+    RotateArgs ra;
+    ra.table = S.rot_tab.as<float2>(); ra.pairs = d.rot_dims / 2; ra.offset = 0; ra.rows = R; ra.row_slot = row_slot; ra.row_pos = row_pos; ra.Smax = kv->max_seq;
+    ra.size = dk;
+    // queries in place, keys into the cache
+    ra.in = qkv; ra.ld_in = ldc; ra.hs_in = dk; ra.out = qkv; ra.ld_out = ldc; ra.hs_out = dk; ra.heads = H;
+    if (ra.pairs > 0) B2_TRY(rotate_rows_f32(ra, st));
+    ra.in = qkv + L.nq; ra.out = nullptr; ra.cache = S.kc.as<float>(); ra.heads = G;
+    B2_TRY(rotate_rows_f32(ra, st));
+    // values into the cache, turned by their own position over all of vdim when the design says so
+    ra.in = qkv + L.nq + L.nk; ra.hs_in = dv; ra.cache = S.vc.as<float>(); ra.size = dv;
+    ra.table = S.vrot_tab.as<float2>(); ra.pairs = d.ga_rot_values ? dv / 2 : 0;
+    B2_TRY(rotate_rows_f32(ra, st));
+    BiasAttnArgs aa;
+    aa.q = qkv; aa.ldq = ldc;
+    aa.kcache = S.kc.as<float>(); aa.vcache = S.vc.as<float>();
+    aa.out = s.y.as<float>(); aa.ldo = L.ng;
+    aa.H = H; aa.G = G; aa.dk = dk; aa.dv = dv; aa.Smax = kv->max_seq; aa.rows = R;
+    aa.scale = d.ga_scale;
+    aa.sink_fixed = d.ga_sink != 0; aa.sink_value = d.ga_sink_value;
+    aa.row_slot = row_slot; aa.row_pos = row_pos;
+    aa.nsplit = attn_nsplit(R, G, kv->max_seq);
+    aa.tile_rows = max_n;
+    if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
+    aa.partial = state.attn_partial.as<float>();
+    mask_of(d, aa);
+    B2_TRY(attn_bias_f32(aa, st));
+    // every head's output is turned back by the query's position, and the sigmoid gate is applied in the same pass
+    RotateArgs rb;
+    rb.in = s.y.as<float>(); rb.ld_in = L.ng; rb.hs_in = dv; rb.out = s.gated.as<float>(); rb.ld_out = L.ng; rb.hs_out = dv;
+    rb.gate = proj + L.nq + L.nk + L.nv; rb.ldg = L.lproj_ld;
+    rb.table = S.vrot_tab.as<float2>(); rb.heads = H; rb.size = dv; rb.offset = 0; rb.pairs = d.ga_rot_values ? dv / 2 : 0; rb.inverse = 1;
+    rb.rows = R; rb.row_pos = row_pos;
+    B2_TRY(rotate_rows_f32(rb, st));
+    return lin(s.gated.as<float>(), L.ng, W.o_w, width, L.ng, target, width, R, LIN_NONE, alpha, accumulate);
+}
+
+// The feed-forward of a pre-norm or sandwich block in its three kinds.
+static int seq_feed_forward(b2_model* m, const SeqLayerInfo& L, SeqWeights& W, const float* h, float* target, float alpha, int accumulate, int R,
+                            cudaStream_t st) {
+    SeqModel& s = *m->seq;
+    const b2_seq_layer_desc& d = L.d;
+    const Lin lin{m, st};
+    const int width = s.d.width;
+    const float eps = s.d.norm_eps;
+    if (d.ff_kind == B2_FF_POLYNORM) {
+        const int ffl = (d.ff + 7) / 8 * 8;
+        B2_TRY(lin(h, width, W.up_w, d.ff, width, s.ff.as<float>(), ffl, R));
+        B2_TRY(polynorm_f32(s.ff.as<float>(), ffl, W.up_b.as<float>(), W.act_coef.as<float>(), s.ffa.as<float>(), d.ff, R, d.ff, eps, st));
+        return lin(s.ffa.as<float>(), d.ff, W.down_w, width, d.ff, target, width, R, LIN_NONE, alpha, accumulate, W.down_b.as<float>(), 0, W.down_b16.p);
+    }
+    if (d.ff_kind != B2_FF_MOE) {
+        B2_TRY(lin(h, width, W.up_w, d.ff, width, s.ff.as<float>(), (d.ff + 7) / 8 * 8, R, LIN_RELU_SQ));
+        return lin(s.ff.as<float>(), (d.ff + 7) / 8 * 8, W.down_w, width, d.ff, target, width, R, LIN_NONE, alpha, accumulate);
+    }
+    const int E = d.moe_experts, top = d.moe_top, ff = d.ff;
+    const bool gated = d.moe_act == B2_MOE_ACT_SWIGLU;
+    const int un = gated ? 2 * ff : ff;   // rows of an expert's first matrix: [gate | up], or up alone
+    const int round_a = s.d.compute == B2_COMPUTE_BF16;
+    B2_TRY(lin(h, width, W.router_w, router_rows(E), width, s.rlogit.as<float>(), router_rows(E), R));
+    MoeRouteArgs ra;
+    ra.logits = s.rlogit.as<float>(); ra.ld = router_rows(E); ra.rows = R; ra.experts = E; ra.top = top;
+    ra.groups = d.moe_groups; ra.keep = d.moe_keep; ra.scale = d.moe_scale;
+    ra.score_fn = d.moe_score; ra.group_score = d.moe_group_score; ra.raw_weights = d.moe_raw_weights;
+    ra.idx = s.moe_idx.as<int32_t>(); ra.w = s.moe_w.as<float>();
+    B2_TRY(moe_route_f32(ra, st));
+    if (d.moe_shared_ff > 0) {
+        const int sf = d.moe_shared_ff;
+        if (!gated) {
+            const int sfl = (sf + 7) / 8 * 8;
+            B2_TRY(lin(h, width, W.sgu_w, sf, width, s.ff.as<float>(), sfl, R, LIN_RELU_SQ));
+            B2_TRY(lin(s.ff.as<float>(), sfl, W.sd_w, width, sf, target, width, R, LIN_NONE, alpha, accumulate));
+        } else {
+            const int sfl = (2 * sf + 7) / 8 * 8;
+            if (R <= 8) {   // decode step: both projections and the gate in one launch (the shared expert is "group 0" of its matrix)
+                GroupedLinearArgs gs;
+                gs.A = h; gs.lda = width; gs.a_div = 1; gs.W = W.sgu_w.p; gs.ldw = width; gs.w_group_stride = 0; gs.w_dtype = s.w_dtype;
+                gs.tile_group = s.zero_idx.as<int32_t>(); gs.tile_rows = 1; gs.out = s.ffa.as<float>(); gs.ld_out = sf;
+                gs.M = R; gs.N = sf; gs.K = width; gs.round_a = round_a; gs.swiglu = 1;
+                B2_TRY(linear_grouped_f32(gs, st));
+            } else {
+                B2_TRY(lin(h, width, W.sgu_w, 2 * sf, width, s.ff.as<float>(), sfl, R));
+                B2_TRY(swiglu_rows_f32(s.ff.as<float>(), sfl, s.ffa.as<float>(), sf, R, sf, st));
+            }
+            B2_TRY(lin(s.ffa.as<float>(), sf, W.sd_w, width, sf, target, width, R, LIN_NONE, alpha, accumulate));
+        }
+    } else if (!accumulate) {
+        B2_CUDA_CHECK(cudaMemsetAsync(target, 0, (size_t)R * width * F4, st));
+    }
+    // routed experts: (token, choice) pairs as rows of grouped products. A decode step keeps the pairs where
+    // they are (tiles of one row); a prompt portion sorts them by expert into tiles of 64 rows.
+    GroupedLinearArgs ga;
+    ga.A = h; ga.lda = width; ga.W = W.egu_w.p; ga.ldw = width; ga.w_group_stride = (int64_t)un * width; ga.w_dtype = s.w_dtype;
+    ga.out = s.moe_h.as<float>(); ga.ld_out = un; ga.N = un; ga.K = width; ga.round_a = round_a;
+    if (!gated) { ga.act = LIN_RELU_SQ; ga.out = s.moe_a.as<float>(); ga.ld_out = ff; }
+    const int32_t* pos = nullptr;
+    int P = R * top;
+    const bool tc = ga.round_a && R >= 64 && tc_enabled() && width % 8 == 0 && ff % 8 == 0 && width >= 32 && ff >= 32;
+    if (R <= 8) {   // decode step: gate, up and the gated activation of a pair in one launch
+        ga.tile_rows = 1; ga.tile_group = s.moe_idx.as<int32_t>(); ga.a_div = top; ga.M = P;
+        if (gated) { ga.swiglu = 1; ga.N = ff; ga.out = s.moe_a.as<float>(); ga.ld_out = ff; }
+    } else {
+        const int tile = tc ? 128 : GROUPED_TILE_ROWS;
+        const int tiles = (R * top + E * (tile - 1) + tile - 1) / tile;
+        B2_TRY(moe_plan(s.moe_idx.as<int32_t>(), R, top, E, tile, tiles, s.moe_pos.as<int32_t>(), s.moe_src.as<int32_t>(),
+                        s.moe_tile.as<int32_t>(), st));
+        pos = s.moe_pos.as<int32_t>();
+        P = tiles * tile;
+        ga.tile_rows = GROUPED_TILE_ROWS; ga.tile_group = s.moe_tile.as<int32_t>(); ga.a_rows = s.moe_src.as<int32_t>(); ga.M = P;
+    }
+    if (tc) {
+        // tensor cores: the sorted pairs' input rows are gathered as bf16, every 128-row tile multiplies with its
+        // expert's rows of the stacked weight matrices in ONE launch per product
+        __nv_bfloat16* a16 = s.moe_a16.as<__nv_bfloat16>();
+        __nv_bfloat16* h16 = a16 + (size_t)s.moe_rows * width;
+        B2_TRY(gather_rows_bf16(h, width, s.moe_src.as<int32_t>(), a16, width, P, width, st));
+        GemmArgs g1;
+        g1.A = a16; g1.lda = width; g1.W = W.egu_w.p; g1.ldw = width; g1.out = s.moe_h.p; g1.ld_out = un; g1.out_fp32 = 1;
+        g1.M = P; g1.N = un; g1.K = width; g1.tile_group = s.moe_tile.as<int32_t>(); g1.groups = E;
+        if (!gated) g1.post = LIN_RELU_SQ;
+        B2_TRY(gemm_bf16(g1, st));
+        if (gated) B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, nullptr, 0, P, ff, st, h16, ff));
+        else B2_TRY(cast_rows_bf16(s.moe_h.as<float>(), ff, h16, ff, P, ff, st));
+        GemmArgs g2;
+        g2.A = h16; g2.lda = ff; g2.W = W.ed_w.p; g2.ldw = ff; g2.out = s.moe_y.p; g2.ld_out = width; g2.out_fp32 = 1;
+        g2.M = P; g2.N = width; g2.K = ff; g2.tile_group = s.moe_tile.as<int32_t>(); g2.groups = E;
+        B2_TRY(gemm_bf16(g2, st));
+    } else {
+        B2_TRY(linear_grouped_f32(ga, st));
+        if (gated && !ga.swiglu) B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, s.moe_a.as<float>(), ff, P, ff, st));
+        GroupedLinearArgs gd = ga;
+        gd.swiglu = 0; gd.act = LIN_NONE;
+        gd.A = s.moe_a.as<float>(); gd.lda = ff; gd.a_rows = nullptr; gd.a_div = 1;
+        gd.W = W.ed_w.p; gd.ldw = ff; gd.w_group_stride = (int64_t)width * ff;
+        gd.out = s.moe_y.as<float>(); gd.ld_out = width; gd.N = width; gd.K = ff;
+        B2_TRY(linear_grouped_f32(gd, st));
+    }
+    return moe_combine_f32(target, s.moe_y.as<float>(), width, pos, s.moe_w.as<float>(), R, top, width, alpha, st);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
 // forward over R rows described by the model's row map (nseg segments). x holds the embedded rows on entry.
 // ------------------------------------------------------------------------------------------------------------------
 // slot / ctx_end: for a prompt portion (nseg == 1) its slot and the slot's length after the call; 0 / 0 for a decode step
@@ -209,7 +494,7 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
     float* mix = s.mixout.as<float>();
     const SeqSeg* segs = s.segs.as<SeqSeg>();
     const int max_n = nseg == 1 ? R : 1;  // a prompt portion is one segment of R rows; a decode step is R segments of one row
-    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1;
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1, sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS;
     const float rm = s.d.residual_mult;
     float* xn = s.xn.as<float>();
     for (size_t ri = 0; ri < s.runs.size(); ++ri) {
@@ -222,72 +507,32 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
         const int pass = s.runs[ri].pass;
         const float* pass_add = pass > 0 ? s.x0.as<float>() : nullptr;
         const float* pass_vec = pass >= 0 ? s.loop_step.as<float>() + (size_t)pass * width : nullptr;
-        if (pre) {
-            // pre-norm block: the mixer reads xn = g1 * unit_rms(x) and adds residual_mult * its output onto x in its last product
-            B2_TRY(rms_scalar_f32(x, nullptr, W.norm1.as<float>(), pass_add, pass_vec, xn, R, width, eps, st));
-            if (d.type == B2_MIXER_LATENT_ATTN) {
-                float* proj = s.proj.as<float>();  // [R, q | dkv | g]
-                const int H = d.la_heads, dk = d.la_dim, dv = d.la_vdim, rank = d.la_rank;
-                B2_TRY(lin(xn, width, W.qdg_w, L.pproj, width, proj, L.pproj_ld, R));
-                B2_TRY(latent_append_f32(proj + L.pq, L.pproj_ld, W.dkv_norm.as<float>(), S.lat.as<float>(), s.row_slot.as<int32_t>(),
-                                         s.row_pos.as<int32_t>(), R, rank, kv->max_seq, eps, st));
-                BiasAttnArgs aa;
-                aa.sink = W.sink.as<float>();
-                aa.H = H; aa.Smax = kv->max_seq; aa.rows = R;
-                aa.eps = eps; aa.scale = d.la_scale; aa.softcap = 0.f;
-                aa.row_slot = s.row_slot.as<int32_t>(); aa.row_pos = s.row_pos.as<int32_t>();
-                aa.tile_rows = max_n;
-                aa.partial = state.attn_partial.as<float>();
-                float* y = s.y.as<float>();
-                if (nseg == 1 && R >= latent_materialise_rows() && ctx_end > 0) {
-                    // a long portion: per-head keys and values of every position of the slot so far are made from the cached
-                    // rows with two products, and the attention runs over them with the heads' own sizes
-                    const float* lat = S.lat.as<float>() + (size_t)slot * kv->max_seq * rank;
-                    for (int m0 = 0; m0 < ctx_end; m0 += s.rows) {
-                        const int mc = std::min(s.rows, ctx_end - m0);
-                        B2_TRY(lin(lat + (size_t)m0 * rank, rank, W.uk_w, L.pq, rank, state.kmat.as<float>() + (size_t)m0 * state.kmat_ld, state.kmat_ld, mc));
-                        B2_TRY(lin(lat + (size_t)m0 * rank, rank, W.uv_w, L.pv, rank, state.vmat.as<float>() + (size_t)m0 * state.vmat_ld, state.vmat_ld, mc));
-                    }
-                    aa.q = proj; aa.ldq = L.pproj_ld;
-                    aa.kcache = state.kmat.as<float>(); aa.vcache = state.vmat.as<float>();
-                    aa.kv_row_stride = state.kmat_ld; aa.kv_row_stride_v = state.vmat_ld;
-                    aa.out = y; aa.ldo = L.pv;
-                    aa.G = H; aa.dk = dk; aa.dv = dv; aa.nsplit = 1;
-                    B2_TRY(attn_bias_f32(aa, st));
-                } else {
-                    // absorbed form: q_h -> W_uk_h^T q_h lives in the latent space, so scores and values read the cached rows
-                    // directly, and W_uv_h carries the latent-space output to the head's values
-                    float* qabs = s.qabs.as<float>();
-                    const int64_t lq = (int64_t)H * rank;
-                    const int round_a = s.d.compute == B2_COMPUTE_BF16;
-                    if (R <= 8) {
-                        B2_TRY(linear_batched_rows_f32(proj, L.pproj_ld, dk, W.ukT.p, (int64_t)rank * dk, s.w_dtype, qabs, lq, rank, H, R, rank, dk, round_a, st));
-                    } else {
-                        for (int h = 0; h < H; ++h)
-                            B2_TRY(lin(proj + (size_t)h * dk, L.pproj_ld, W.ukT, rank, dk, qabs + (size_t)h * rank, lq, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * rank));
-                    }
-                    aa.q = qabs; aa.ldq = lq;
-                    aa.kcache = S.lat.as<float>(); aa.vcache = S.lat.as<float>();
-                    aa.out = s.olat.as<float>(); aa.ldo = lq;
-                    aa.G = 1; aa.dk = rank; aa.dv = rank;
-                    aa.nsplit = attn_nsplit(R, (H + 31) / 32, kv->max_seq);
-                    if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
-                    B2_TRY(attn_bias_f32(aa, st));
-                    if (R <= 8) {   // with the heads' sigmoid gates in the same launch
-                        y = s.gated.as<float>();
-                        B2_TRY(linear_batched_rows_f32(s.olat.as<float>(), lq, rank, W.uv_w.p, (int64_t)dv * rank, s.w_dtype, y, L.pv, dv, H, R, dv, rank, round_a, st,
-                                                       proj + L.pq + rank, L.pproj_ld));
-                    } else {
-                        for (int h = 0; h < H; ++h)
-                            B2_TRY(lin(s.olat.as<float>() + (size_t)h * rank, lq, W.uv_w, dv, rank, y + (size_t)h * dv, L.pv, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * dv));
-                    }
+        if (pre || sandwich) {
+            // pre-norm block: a sublayer reads g * unit_rms(x) and adds residual_mult * its output onto x in its last product.
+            // sandwich block: a sublayer reads u + conv(u), u = rms_w(x); its output lands in `mix` and its weighted RMS norm joins x.
+            const int ctaps = s.d.input_conv_taps;
+            float* target = pre ? x : mix;
+            const float alpha = pre ? rm : 1.f;
+            const float* h = xn;
+            if (pre) {
+                B2_TRY(rms_scalar_f32(x, nullptr, W.norm1.as<float>(), pass_add, pass_vec, xn, R, width, eps, st));
+            } else {
+                B2_TRY(rms_weight_f32(x, width, nullptr, W.norm1.as<float>(), xn, width, 0, R, width, eps, st));
+                if (ctaps > 1) {
+                    B2_TRY(causal_conv_f32(xn, width, W.canon1.as<float>(), nullptr, S.canon1.as<float>(), s.hin.as<float>(), width, width, ctaps, CONV_ADD_INPUT,
+                                           segs, nseg, max_n, st));
+                    h = s.hin.as<float>();
                 }
-                if (y != s.gated.as<float>()) B2_TRY(head_gate_f32(y, L.pv, proj + L.pq + rank, L.pproj_ld, s.gated.as<float>(), L.pv, R, H, dv, st));
-                B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, x, width, R, LIN_NONE, rm, 1));
+            }
+            if (d.type == B2_MIXER_LATENT_ATTN) {
+                SeqLayerState& KS = d.la_kv_from > 0 ? state.layer[s.runs[ri].kv_run] : S;
+                B2_TRY(latent_mixer(m, kv, L, W, S, KS, h, target, alpha, pre ? 1 : 0, R, nseg, slot, ctx_end, st));
+            } else if (d.type == B2_MIXER_GQA_ATTN) {
+                B2_TRY(gqa_mixer(m, kv, L, W, S, h, target, alpha, pre ? 1 : 0, R, nseg, st));
             } else {
                 float* proj = s.proj.as<float>();  // [R, q | f | v]
                 const int H = d.g_heads, dk = d.g_dim, dv = d.g_vdim;
-                B2_TRY(lin(xn, width, W.qfv_w, L.pproj, width, proj, L.pproj_ld, R));
+                B2_TRY(lin(h, width, W.qfv_w, L.pproj, width, proj, L.pproj_ld, R));
                 ScanArgs sa;
                 sa.mode = SCAN_HGRN2;
                 sa.q = proj; sa.ldq = L.pproj_ld;
@@ -300,87 +545,23 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                 sa.segs = segs; sa.nseg = nseg;
                 B2_TRY(linear_scan_f32(sa, st));
                 B2_TRY(group_rmsnorm_f32(s.y.as<float>(), L.pv, W.hnorm.as<float>(), 1, s.gated.as<float>(), L.pv, R, L.pv, dv, eps, st));
-                B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, x, width, R, LIN_NONE, rm, 1));
+                B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, target, width, R, LIN_NONE, alpha, pre ? 1 : 0));
             }
+            if (sandwich) B2_TRY(rms_weight_f32(mix, width, nullptr, W.norm1_b.as<float>(), x, width, 1, R, width, eps, st));
             if (d.ff > 0) {
-                B2_TRY(rms_scalar_f32(x, nullptr, W.norm2.as<float>(), nullptr, nullptr, xn, R, width, eps, st));
-                if (d.ff_kind == B2_FF_POLYNORM) {
-                    const int ffl = (d.ff + 7) / 8 * 8;
-                    B2_TRY(lin(xn, width, W.up_w, d.ff, width, s.ff.as<float>(), ffl, R));
-                    B2_TRY(polynorm_f32(s.ff.as<float>(), ffl, W.up_b.as<float>(), W.act_coef.as<float>(), s.ffa.as<float>(), d.ff, R, d.ff, eps, st));
-                    B2_TRY(lin(s.ffa.as<float>(), d.ff, W.down_w, width, d.ff, x, width, R, LIN_NONE, rm, 1, W.down_b.as<float>(), 0, W.down_b16.p));
-                } else if (d.ff_kind == B2_FF_MOE) {
-                    const int E = d.moe_experts, top = d.moe_top, ff = d.ff;
-                    B2_TRY(lin(xn, width, W.router_w, router_rows(E), width, s.rlogit.as<float>(), router_rows(E), R));
-                    MoeRouteArgs ra;
-                    ra.logits = s.rlogit.as<float>(); ra.ld = router_rows(E); ra.rows = R; ra.experts = E; ra.top = top;
-                    ra.groups = d.moe_groups; ra.keep = d.moe_keep; ra.scale = d.moe_scale;
-                    ra.idx = s.moe_idx.as<int32_t>(); ra.w = s.moe_w.as<float>();
-                    B2_TRY(moe_route_f32(ra, st));
-                    if (d.moe_shared_ff > 0) {
-                        const int sf = d.moe_shared_ff, sfl = (2 * sf + 7) / 8 * 8;
-                        if (R <= 8) {   // decode step: both projections and the gate in one launch (the shared expert is "group 0" of its matrix)
-                            GroupedLinearArgs gs;
-                            gs.A = xn; gs.lda = width; gs.a_div = 1; gs.W = W.sgu_w.p; gs.ldw = width; gs.w_group_stride = 0; gs.w_dtype = s.w_dtype;
-                            gs.tile_group = s.zero_idx.as<int32_t>(); gs.tile_rows = 1; gs.out = s.ffa.as<float>(); gs.ld_out = sf;
-                            gs.M = R; gs.N = sf; gs.K = width; gs.round_a = s.d.compute == B2_COMPUTE_BF16; gs.swiglu = 1;
-                            B2_TRY(linear_grouped_f32(gs, st));
-                        } else {
-                            B2_TRY(lin(xn, width, W.sgu_w, 2 * sf, width, s.ff.as<float>(), sfl, R));
-                            B2_TRY(swiglu_rows_f32(s.ff.as<float>(), sfl, s.ffa.as<float>(), sf, R, sf, st));
-                        }
-                        B2_TRY(lin(s.ffa.as<float>(), sf, W.sd_w, width, sf, x, width, R, LIN_NONE, rm, 1));
-                    }
-                    // routed experts: (token, choice) pairs as rows of grouped products. A decode step keeps the pairs where
-                    // they are (tiles of one row); a prompt portion sorts them by expert into tiles of 64 rows.
-                    GroupedLinearArgs ga;
-                    ga.A = xn; ga.lda = width; ga.W = W.egu_w.p; ga.ldw = width; ga.w_group_stride = (int64_t)2 * ff * width; ga.w_dtype = s.w_dtype;
-                    ga.out = s.moe_h.as<float>(); ga.ld_out = 2 * ff; ga.N = 2 * ff; ga.K = width; ga.round_a = s.d.compute == B2_COMPUTE_BF16;
-                    const int32_t* pos = nullptr;
-                    int P = R * top;
-                    const bool tc = ga.round_a && R >= 64 && tc_enabled() && width % 8 == 0 && ff % 8 == 0 && width >= 32 && ff >= 32;
-                    if (R <= 8) {   // decode step: gate, up and the gated activation of a pair in one launch
-                        ga.tile_rows = 1; ga.tile_group = s.moe_idx.as<int32_t>(); ga.a_div = top; ga.M = P;
-                        ga.swiglu = 1; ga.N = ff; ga.out = s.moe_a.as<float>(); ga.ld_out = ff;
-                    } else {
-                        const int tile = tc ? 128 : GROUPED_TILE_ROWS;
-                        const int tiles = (R * top + E * (tile - 1) + tile - 1) / tile;
-                        B2_TRY(moe_plan(s.moe_idx.as<int32_t>(), R, top, E, tile, tiles, s.moe_pos.as<int32_t>(), s.moe_src.as<int32_t>(),
-                                        s.moe_tile.as<int32_t>(), st));
-                        pos = s.moe_pos.as<int32_t>();
-                        P = tiles * tile;
-                        ga.tile_rows = GROUPED_TILE_ROWS; ga.tile_group = s.moe_tile.as<int32_t>(); ga.a_rows = s.moe_src.as<int32_t>(); ga.M = P;
-                    }
-                    if (tc) {
-                        // tensor cores: the sorted pairs' input rows are gathered as bf16, every 128-row tile multiplies with its
-                        // expert's rows of the stacked weight matrices in ONE launch per product
-                        __nv_bfloat16* a16 = s.moe_a16.as<__nv_bfloat16>();
-                        __nv_bfloat16* h16 = a16 + (size_t)s.moe_rows * width;
-                        B2_TRY(gather_rows_bf16(xn, width, s.moe_src.as<int32_t>(), a16, width, P, width, st));
-                        GemmArgs g1;
-                        g1.A = a16; g1.lda = width; g1.W = W.egu_w.p; g1.ldw = width; g1.out = s.moe_h.p; g1.ld_out = 2 * ff; g1.out_fp32 = 1;
-                        g1.M = P; g1.N = 2 * ff; g1.K = width; g1.tile_group = s.moe_tile.as<int32_t>(); g1.groups = E;
-                        B2_TRY(gemm_bf16(g1, st));
-                        B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, nullptr, 0, P, ff, st, h16, ff));
-                        GemmArgs g2;
-                        g2.A = h16; g2.lda = ff; g2.W = W.ed_w.p; g2.ldw = ff; g2.out = s.moe_y.p; g2.ld_out = width; g2.out_fp32 = 1;
-                        g2.M = P; g2.N = width; g2.K = ff; g2.tile_group = s.moe_tile.as<int32_t>(); g2.groups = E;
-                        B2_TRY(gemm_bf16(g2, st));
-                    } else {
-                        B2_TRY(linear_grouped_f32(ga, st));
-                        if (!ga.swiglu) B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, s.moe_a.as<float>(), ff, P, ff, st));
-                        GroupedLinearArgs gd = ga;
-                        gd.swiglu = 0;
-                        gd.A = s.moe_a.as<float>(); gd.lda = ff; gd.a_rows = nullptr; gd.a_div = 1;
-                        gd.W = W.ed_w.p; gd.ldw = ff; gd.w_group_stride = (int64_t)width * ff;
-                        gd.out = s.moe_y.as<float>(); gd.ld_out = width; gd.N = width; gd.K = ff;
-                        B2_TRY(linear_grouped_f32(gd, st));
-                    }
-                    B2_TRY(moe_combine_f32(x, s.moe_y.as<float>(), width, pos, s.moe_w.as<float>(), R, top, width, rm, st));
+                h = xn;
+                if (pre) {
+                    B2_TRY(rms_scalar_f32(x, nullptr, W.norm2.as<float>(), nullptr, nullptr, xn, R, width, eps, st));
                 } else {
-                    B2_TRY(lin(xn, width, W.up_w, d.ff, width, s.ff.as<float>(), (d.ff + 7) / 8 * 8, R, LIN_RELU_SQ));
-                    B2_TRY(lin(s.ff.as<float>(), (d.ff + 7) / 8 * 8, W.down_w, width, d.ff, x, width, R, LIN_NONE, rm, 1));
+                    B2_TRY(rms_weight_f32(x, width, nullptr, W.norm2.as<float>(), xn, width, 0, R, width, eps, st));
+                    if (ctaps > 1) {
+                        B2_TRY(causal_conv_f32(xn, width, W.canon2.as<float>(), nullptr, S.canon2.as<float>(), s.hin.as<float>(), width, width, ctaps,
+                                               CONV_ADD_INPUT, segs, nseg, max_n, st));
+                        h = s.hin.as<float>();
+                    }
                 }
+                B2_TRY(seq_feed_forward(m, L, W, h, target, alpha, pre ? 1 : 0, R, st));
+                if (sandwich) B2_TRY(rms_weight_f32(mix, width, nullptr, W.norm2_b.as<float>(), x, width, 1, R, width, eps, st));
             }
             if (resid_out != nullptr)
                 B2_CUDA_CHECK(cudaMemcpyAsync(resid_out + ri * (size_t)R * width, x, (size_t)R * width * F4, cudaMemcpyDeviceToDevice, st));
@@ -486,10 +667,12 @@ static int seq_head(b2_model* m, const int32_t* index, int n, float* logits, int
     SeqModel& s = *m->seq;
     if (s.d.block == B2_BLOCK_PRE_RMS1)
         B2_TRY(rms_scalar_f32(s.x.as<float>(), index, s.final_w.as<float>(), nullptr, nullptr, s.xn.as<float>(), n, s.d.width, s.d.norm_eps, st));
+    else if (s.d.block == B2_BLOCK_SANDWICH_RMS)
+        B2_TRY(rms_weight_f32(s.x.as<float>(), s.d.width, index, s.final_w.as<float>(), s.xn.as<float>(), s.d.width, 0, n, s.d.width, s.d.norm_eps, st));
     else
         B2_TRY(layernorm_gather_f32(s.x.as<float>(), index, s.final_w.as<float>(), s.final_b.as<float>(), s.xn.as<float>(), n, s.d.width, s.d.norm_eps, st));
     const Lin lin{m, st};
-    B2_TRY(lin(s.xn.as<float>(), s.d.width, s.head, s.d.vocab, s.d.width, logits, ld, n));
+    B2_TRY(lin(s.xn.as<float>(), s.d.width, s.head, s.d.vocab, s.d.width, logits, ld, n, LIN_NONE, s.d.logit_scale != 0.f ? s.d.logit_scale : 1.f));
     if (s.d.logit_softcap > 0.f) {
         B2_CHECK_ARG(ld == s.d.vocab, "seq_head: soft-capped logits are contiguous rows");
         B2_TRY(softcap_f32(logits, (size_t)n * s.d.vocab, s.d.logit_softcap, st));
@@ -520,8 +703,9 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     const std::string k(key);
     if (k == "embed") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.embed, WD, (size_t)V * width, 0, ptr, dt, (int64_t)V * width); }
     if (k == "head") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.head, WD, (size_t)((V + 7) / 8 * 8) * width, 0, ptr, dt, (int64_t)V * width); }
-    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1;
-    if (k == "final.norm" && pre) { B2_TRY(want_shape(key, shape, ndim, 1)); s.got[k] = 1; return put_tensor(s.final_w, DT_F32, 1, 0, ptr, dt, 1); }
+    const bool sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS;
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1 || sandwich;   // blocks whose layers are made of the mixers / feed-forwards below
+    if (k == "final.norm" && pre && !sandwich) { B2_TRY(want_shape(key, shape, ndim, 1)); s.got[k] = 1; return put_tensor(s.final_w, DT_F32, 1, 0, ptr, dt, 1); }
     if (k == "bigram" && s.d.bigram_buckets > 0) {
         const int64_t rows = (int64_t)s.d.bigram_buckets + 1;
         B2_TRY(want_shape(key, shape, ndim, rows, width)); s.got[k] = 1;
@@ -553,15 +737,36 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
             W.got[r] = 1;
             return put_tensor(b, WD, (size_t)((total_rows + 7) / 8 * 8) * cols, (size_t)row0 * cols, ptr, dt, (int64_t)rows * cols);
         };
-        if (r == "norm1") return vec(W.norm1, 1);
-        if (r == "norm2" && d.ff > 0) return vec(W.norm2, 1);
+        auto taps_of = [&](DevBuf& b, int64_t ch, int64_t total_ch, int64_t ch0, int taps) -> int {   // [channels][taps] at its channel offset
+            B2_TRY(want_shape(key, shape, ndim, ch, taps));
+            W.got[r] = 1;
+            return put_tensor(b, DT_F32, (size_t)total_ch * taps, (size_t)ch0 * taps, ptr, dt, ch * taps);
+        };
+        if (sandwich) {
+            const int ct = s.d.input_conv_taps;
+            if (r == "norm1") return vec(W.norm1, width);
+            if (r == "norm1b") return vec(W.norm1_b, width);
+            if (r == "canon1" && ct > 1) return taps_of(W.canon1, width, width, 0, ct);
+            if (d.ff > 0) {
+                if (r == "norm2") return vec(W.norm2, width);
+                if (r == "norm2b") return vec(W.norm2_b, width);
+                if (r == "canon2" && ct > 1) return taps_of(W.canon2, width, width, 0, ct);
+            }
+        } else {
+            if (r == "norm1") return vec(W.norm1, 1);
+            if (r == "norm2" && d.ff > 0) return vec(W.norm2, 1);
+        }
         if (d.type == B2_MIXER_LATENT_ATTN) {
-            const int H = d.la_heads, dk = d.la_dim, dv = d.la_vdim, rank = d.la_rank;
-            if (r == "mix.q") return part(W.qdg_w, L.pproj, 0, L.pq, width);
-            if (r == "mix.dkv") return part(W.qdg_w, L.pproj, L.pq, rank, width);
-            if (r == "mix.g") return part(W.qdg_w, L.pproj, L.pq + rank, H, width);
-            if (r == "mix.dkv.norm") return vec(W.dkv_norm, rank);
-            if (r == "mix.sink") return vec(W.sink, H);
+            const int H = d.la_heads, dk = d.la_dim, dv = d.la_vdim, rank = d.la_rank, rd = d.la_rot_dim;
+            const bool own = d.la_kv_from == 0;
+            if (r == "mix.q" && d.la_q_rank == 0) return part(W.qdg_w, L.pproj, 0, L.pq, width);
+            if (r == "mix.dq" && d.la_q_rank > 0) return part(W.qdg_w, L.pproj, 0, L.pq, width);
+            if (r == "mix.dq.norm" && d.la_q_rank > 0) return vec(W.dq_norm, d.la_q_rank);
+            if (r == "mix.uq" && d.la_q_rank > 0) return mat(W.uq_w, L.lqw, d.la_q_rank);
+            if (r == "mix.dkv" && own) return part(W.qdg_w, L.pproj, L.pq, L.lrow, width);
+            if (r == "mix.g" && !d.la_no_gate) return part(W.qdg_w, L.pproj, L.pq + (own ? L.lrow : 0), H, width);
+            if (r == "mix.dkv.norm" && own) return vec(W.dkv_norm, rank);
+            if (r == "mix.sink" && !d.la_no_sink) return vec(W.sink, H);
             if (r == "mix.uv") return mat(W.uv_w, (int64_t)H * dv, rank);
             if (r == "mix.o") return mat(W.o_w, width, (int64_t)H * dv);
             if (r == "mix.uk") {
@@ -572,8 +777,37 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
                 if (rc == 0) rc = cudaMemset(W.ukT.p, 0, W.ukT.bytes) == cudaSuccess ? 0 : -2;
                 if (rc == 0) rc = transpose_blocks(W.uk_w.p, W.ukT.p, H, dk, rank, (int)esz(WD), 0);
                 cudaStreamSynchronize(0);
-                return rc;
+                if (rc != 0 || rd == 0) return rc;
+                // with a rotated key part: head h's rows [W_uk_h 0; 0 I], so that ONE product over the cached rows [c | rotated part]
+                // gives every head's whole key
+                const size_t e = esz(WD), lrow = (size_t)L.lrow, qh = (size_t)dk + rd;
+                B2_TRY(W.ukx_w.alloc(((size_t)H * qh + 8) * lrow * e));
+                B2_CUDA_CHECK(cudaMemset(W.ukx_w.p, 0, W.ukx_w.bytes));
+                std::vector<unsigned char> eye((size_t)rd * rd * e, 0);
+                for (int i = 0; i < rd; ++i) {
+                    if (WD == DT_F32) reinterpret_cast<float*>(eye.data())[(size_t)i * rd + i] = 1.f;
+                    else reinterpret_cast<uint16_t*>(eye.data())[(size_t)i * rd + i] = 0x3F80;   // 1.0 as bfloat16
+                }
+                for (int hh = 0; hh < H; ++hh) {
+                    char* dst = W.ukx_w.as<char>() + (size_t)hh * qh * lrow * e;
+                    B2_CUDA_CHECK(cudaMemcpy2D(dst, lrow * e, W.uk_w.as<char>() + (size_t)hh * dk * rank * e, (size_t)rank * e, (size_t)rank * e, dk,
+                                               cudaMemcpyDeviceToDevice));
+                    B2_CUDA_CHECK(cudaMemcpy2D(dst + ((size_t)dk * lrow + rank) * e, lrow * e, eye.data(), (size_t)rd * e, (size_t)rd * e, rd,
+                                               cudaMemcpyHostToDevice));
+                }
+                return 0;
             }
+        } else if (d.type == B2_MIXER_GQA_ATTN) {
+            // the four projections share their input: one [nq + nk + nv + ng, width] matrix, one product; the taps of q, k, v side by side
+            const char* parts[4] = {"mix.q", "mix.k", "mix.v", "mix.g"};
+            const int sizes[4] = {L.nq, L.nk, L.nv, L.ng};
+            int row0 = 0;
+            for (int j = 0; j < 4; ++j) {
+                if (r == parts[j]) return part(W.lproj_w, L.lproj, row0, sizes[j], width);
+                if (j < 3 && d.ga_conv > 1 && r == std::string(parts[j]) + ".conv") return taps_of(W.conv_w, sizes[j], L.conv_ch, row0, d.ga_conv);
+                row0 += sizes[j];
+            }
+            if (r == "mix.o") return mat(W.o_w, width, L.ng);
         } else if (d.type == B2_MIXER_HGRN2) {
             const int H = d.g_heads, dk = d.g_dim, dv = d.g_vdim;
             if (r == "mix.q") return part(W.qfv_w, L.pproj, 0, L.pq, width);
@@ -595,24 +829,27 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
             }
         } else if (d.ff > 0 && d.ff_kind == B2_FF_MOE) {
             const int E = d.moe_experts, ff = d.ff, sf = d.moe_shared_ff;
+            const bool gated = d.moe_act == B2_MOE_ACT_SWIGLU;
+            const int un = gated ? 2 : 1;   // matrices in front of an expert's activation
             if (r == "mlp.router") {   // at least 32 rows (zeros behind the experts): the tensor-core product of a prompt portion takes it
                 B2_TRY(want_shape(key, shape, ndim, E, width));
                 W.got[r] = 1;
                 return put_tensor(W.router_w, WD, (size_t)router_rows(E) * width, 0, ptr, dt, (int64_t)E * width);
             }
             if (sf > 0) {
-                if (r == "mlp.shared.gate") return part(W.sgu_w, 2 * sf, 0, sf, width);
-                if (r == "mlp.shared.up") return part(W.sgu_w, 2 * sf, sf, sf, width);
+                if (r == "mlp.shared.gate" && gated) return part(W.sgu_w, 2 * sf, 0, sf, width);
+                if (r == "mlp.shared.up") return part(W.sgu_w, un * sf, gated ? sf : 0, sf, width);
                 if (r == "mlp.shared.down") return mat(W.sd_w, width, sf);
             }
             int e = -1, eu = 0;
             if (sscanf(r.c_str(), "mlp.e%d.%n", &e, &eu) == 1 && eu > 0 && e >= 0 && e < E) {
                 const std::string which = r.substr(eu);
                 // experts side by side: [E][gate | up][width] and [E][width][ff] (8 spare rows behind the last one)
-                if (which == "gate" || which == "up") {
+                if ((which == "gate" && gated) || which == "up") {
                     B2_TRY(want_shape(key, shape, ndim, ff, width));
                     W.got[r] = 1;
-                    return put_tensor(W.egu_w, WD, ((size_t)E * 2 * ff + 8) * width, ((size_t)e * 2 + (which == "up")) * ff * width, ptr, dt, (int64_t)ff * width);
+                    return put_tensor(W.egu_w, WD, ((size_t)E * un * ff + 8) * width, ((size_t)e * un + (gated && which == "up")) * ff * width, ptr, dt,
+                                      (int64_t)ff * width);
                 }
                 if (which == "down") {
                     B2_TRY(want_shape(key, shape, ndim, width, ff));
@@ -681,19 +918,35 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     return -1;
 }
 
-static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre) {
+static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre, bool sandwich, int ctaps) {
     if (pre) {
-        std::vector<std::string> v = {"norm1", "mix.q", "mix.o"};
-        if (L.d.type == B2_MIXER_LATENT_ATTN) for (const char* n : {"mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv", "mix.sink", "mix.g"}) v.push_back(n);
-        else for (const char* n : {"mix.f", "mix.f.b", "mix.lower", "mix.v", "mix.norm"}) v.push_back(n);
+        std::vector<std::string> v = {"norm1", "mix.o"};
+        const b2_seq_layer_desc& d = L.d;
+        if (sandwich) { v.push_back("norm1b"); if (ctaps > 1) v.push_back("canon1"); }
+        if (d.type == B2_MIXER_LATENT_ATTN) {
+            for (const char* n : {"mix.uk", "mix.uv"}) v.push_back(n);
+            if (d.la_q_rank > 0) for (const char* n : {"mix.dq", "mix.dq.norm", "mix.uq"}) v.push_back(n);
+            else v.push_back("mix.q");
+            if (d.la_kv_from == 0) for (const char* n : {"mix.dkv", "mix.dkv.norm"}) v.push_back(n);
+            if (!d.la_no_sink) v.push_back("mix.sink");
+            if (!d.la_no_gate) v.push_back("mix.g");
+        } else if (d.type == B2_MIXER_GQA_ATTN) {
+            for (const char* n : {"mix.q", "mix.k", "mix.v", "mix.g"}) v.push_back(n);
+            if (d.ga_conv > 1) for (const char* n : {"mix.q.conv", "mix.k.conv", "mix.v.conv"}) v.push_back(n);
+        } else for (const char* n : {"mix.q", "mix.f", "mix.f.b", "mix.lower", "mix.v", "mix.norm"}) v.push_back(n);
         if (L.d.ff > 0) {
             v.push_back("norm2");
+            if (sandwich) { v.push_back("norm2b"); if (ctaps > 1) v.push_back("canon2"); }
             if (L.d.ff_kind == B2_FF_POLYNORM) for (const char* n : {"mlp.up", "mlp.up.b", "mlp.down", "mlp.down.b", "mlp.act"}) v.push_back(n);
             else if (L.d.ff_kind == B2_FF_MOE) {
                 v.push_back("mlp.router");
+                const bool gated = L.d.moe_act == B2_MOE_ACT_SWIGLU;
                 for (int e = 0; e < L.d.moe_experts; ++e)
-                    for (const char* n : {"gate", "up", "down"}) v.push_back("mlp.e" + std::to_string(e) + "." + n);
-                if (L.d.moe_shared_ff > 0) for (const char* n : {"mlp.shared.gate", "mlp.shared.up", "mlp.shared.down"}) v.push_back(n);
+                    for (const char* n : {"gate", "up", "down"})
+                        if (gated || n[0] != 'g') v.push_back("mlp.e" + std::to_string(e) + "." + n);
+                if (L.d.moe_shared_ff > 0)
+                    for (const char* n : {"mlp.shared.gate", "mlp.shared.up", "mlp.shared.down"})
+                        if (gated || n[11] != 'g') v.push_back(n);
             } else for (const char* n : {"mlp.up", "mlp.down"}) v.push_back(n);
         }
         return v;
@@ -714,7 +967,8 @@ static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre) {
 int seq_finalize(b2_model* m) {
     SeqModel& s = *m->seq;
     std::string missing;
-    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1;
+    const bool sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS;
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1 || sandwich;
     std::vector<std::string> top = {"embed", "head", "final.norm"};
     if (!pre) top.push_back("final.norm.b");
     if (s.d.bigram_buckets > 0) top.push_back("bigram");
@@ -723,7 +977,7 @@ int seq_finalize(b2_model* m) {
         if (!s.got.count(n) && missing.size() < 600) { missing += n; missing += ' '; }
     for (size_t i = 0; i < s.layers.size(); ++i) {
         if (s.layers[i].src != (int)i) continue;
-        for (const std::string& n : required_of(s.layers[i], pre))
+        for (const std::string& n : required_of(s.layers[i], pre, sandwich, s.d.input_conv_taps))
             if (!s.w[i].got.count(n) && missing.size() < 600) missing += "l" + std::to_string(i) + "." + n + " ";
     }
     if (!missing.empty()) {
@@ -738,9 +992,14 @@ int seq_finalize(b2_model* m) {
             pw = std::max(pw, L.dproj_ld); aw = std::max(aw, L.conv_ch); yw = std::max(yw, L.inner);
         } else if (L.d.type == B2_MIXER_PARALLEL) {
             pw = std::max(pw, L.lproj_ld); yw = std::max(yw, std::max(L.ng, L.rn)); rw = std::max(rw, L.rn); kw = std::max(kw, L.d.r_decay_rank);
+        } else if (L.d.type == B2_MIXER_GQA_ATTN) {
+            pw = std::max(pw, L.lproj_ld); yw = std::max(yw, L.ng); aw = std::max(aw, L.conv_ch);
         } else {
             pw = std::max(pw, L.pproj_ld); yw = std::max(yw, L.pv);
-            if (L.d.type == B2_MIXER_LATENT_ATTN) latw = std::max(latw, L.d.la_heads * L.d.la_rank);
+            if (L.d.type == B2_MIXER_LATENT_ATTN) {
+                latw = std::max(latw, L.d.la_heads * L.lrow);
+                if (L.d.la_q_rank > 0) aw = std::max(aw, L.lqw_ld);
+            }
         }
         fw = std::max(fw, (L.d.ff + 7) / 8 * 8);
         if (L.d.ff > 0 && L.d.ff_kind == B2_FF_MOE) {
@@ -764,6 +1023,7 @@ int seq_finalize(b2_model* m) {
     B2_TRY(s.ff.alloc(R * fw * F4));
     B2_TRY(s.xn.alloc(R * width * F4));
     if (pre) B2_TRY(s.ffa.alloc(R * fw * F4));
+    if (sandwich && s.d.input_conv_taps > 1) B2_TRY(s.hin.alloc(R * width * F4));
     if (s.d.loop_times > 1) B2_TRY(s.x0.alloc(R * width * F4));
     if (latw > 0) {
         s.lat_w = latw;
@@ -793,7 +1053,7 @@ int seq_finalize(b2_model* m) {
     {
         int kmax = width;
         for (const SeqLayerInfo& L : s.layers)
-            kmax = std::max(kmax, std::max(std::max(std::max(L.inner, L.ng), std::max(L.rn, L.d.ff)), std::max(std::max(L.pv, L.d.la_rank), std::max(L.d.la_dim, L.d.moe_shared_ff))));
+            kmax = std::max(kmax, std::max(std::max(std::max(L.inner, L.ng), std::max(L.rn, L.d.ff)), std::max(std::max(L.pv, std::max(L.lrow, L.d.la_q_rank)), std::max(L.d.la_dim, L.d.moe_shared_ff))));
         s.a16_w = (kmax + 7) / 8 * 8;
         if (s.d.compute == B2_COMPUTE_BF16) B2_TRY(s.a16.alloc(R * s.a16_w * 2));
     }
@@ -813,12 +1073,12 @@ void seq_model_free(b2_model* m) {
         DevBuf* bs[] = {&W.norm1, &W.norm1_b, &W.norm2, &W.norm2_b, &W.in_w, &W.conv_w, &W.conv_b, &W.dt_bias, &W.a_log, &W.skip, &W.mnorm, &W.o_w,
                         &W.lproj_w, &W.rel, &W.lo_w, &W.mu, &W.r_w, &W.k_w, &W.v_w, &W.g_w, &W.w1, &W.w2, &W.w0, &W.bonus, &W.rnorm, &W.ro_w,
                         &W.up_w, &W.down_w, &W.qdg_w, &W.dkv_norm, &W.uk_w, &W.ukT, &W.uv_w, &W.sink, &W.qfv_w, &W.f_b, &W.lower, &W.hnorm, &W.up_b, &W.down_b,
-                        &W.down_b16, &W.act_coef, &W.router_w, &W.egu_w, &W.ed_w, &W.sgu_w, &W.sd_w};
+                        &W.down_b16, &W.act_coef, &W.router_w, &W.egu_w, &W.ed_w, &W.sgu_w, &W.sd_w, &W.canon1, &W.canon2, &W.dq_norm, &W.uq_w, &W.ukx_w};
         for (DevBuf* b : bs) b->free();
     }
     DevBuf* bs[] = {&s.embed, &s.head, &s.final_w, &s.final_b, &s.x, &s.proj, &s.act, &s.y, &s.gated, &s.mixout, &s.mixes, &s.rp, &s.wl1, &s.wlog,
                     &s.ff, &s.xn, &s.tok, &s.want, &s.segs, &s.row_slot, &s.row_pos, &s.a16, &s.bigram, &s.loop_step, &s.x0, &s.qabs, &s.olat, &s.ffa,
-                    &s.rlogit, &s.moe_idx, &s.moe_w, &s.moe_pos, &s.moe_src, &s.moe_tile, &s.moe_h, &s.moe_a, &s.moe_y, &s.moe_a16, &s.zero_idx};
+                    &s.rlogit, &s.moe_idx, &s.moe_w, &s.moe_pos, &s.moe_src, &s.moe_tile, &s.moe_h, &s.moe_a, &s.moe_y, &s.moe_a16, &s.zero_idx, &s.hin};
     for (DevBuf* b : bs) b->free();
     delete m->seq;
     m->seq = nullptr;
@@ -843,8 +1103,11 @@ int64_t seq_kv_bytes(const b2_model* m, int B, int Smax) {
         if (d.type == B2_MIXER_MAMBA2) n += (int64_t)B * d.m_heads * d.m_state * d.m_vdim + (int64_t)B * (d.m_conv - 1) * L.conv_ch;
         else if (d.type == B2_MIXER_PARALLEL)
             n += (int64_t)B * d.a_kv_heads * Smax * (d.a_dim + d.a_vdim) + (int64_t)B * d.r_heads * d.r_dim * d.r_dim + (int64_t)B * m->seq->d.width;
-        else if (d.type == B2_MIXER_LATENT_ATTN) n += (int64_t)B * Smax * d.la_rank;
+        else if (d.type == B2_MIXER_LATENT_ATTN) n += d.la_kv_from == 0 ? (int64_t)B * Smax * L.lrow : 0;
+        else if (d.type == B2_MIXER_GQA_ATTN) n += (int64_t)B * d.ga_kv_heads * Smax * (d.ga_dim + d.ga_vdim) + (int64_t)B * std::max(0, d.ga_conv - 1) * L.conv_ch;
         else n += (int64_t)B * d.g_heads * d.g_dim * d.g_vdim;
+        if (m->seq->d.block == B2_BLOCK_SANDWICH_RMS && m->seq->d.input_conv_taps > 1)
+            n += (int64_t)B * (m->seq->d.input_conv_taps - 1) * m->seq->d.width * (d.ff > 0 ? 2 : 1);
     }
     return n * 4 + (m->seq->d.bigram_buckets > 0 ? (int64_t)B * 4 : 0);
 }
@@ -862,9 +1125,44 @@ int seq_kv_alloc(b2_kv* kv) {
         const SeqLayerInfo& L = s.layers[s.runs[li].layer];
         const b2_seq_layer_desc& d = L.d;
         SeqLayerState& S = kv->seq->layer[li];
-        if (d.type == B2_MIXER_LATENT_ATTN) {
-            B2_TRY(S.lat.alloc(B * Smax * d.la_rank * F4));
-            cudaMemset(S.lat.p, 0, S.lat.bytes);
+        if (s.d.block == B2_BLOCK_SANDWICH_RMS && s.d.input_conv_taps > 1) {
+            const size_t n = B * (s.d.input_conv_taps - 1) * s.d.width * F4;
+            B2_TRY(S.canon1.alloc(n));
+            cudaMemset(S.canon1.p, 0, n);
+            if (d.ff > 0) {
+                B2_TRY(S.canon2.alloc(n));
+                cudaMemset(S.canon2.p, 0, n);
+            }
+        }
+        if (d.rot_dims > 0 && (d.type == B2_MIXER_GQA_ATTN || (d.type == B2_MIXER_LATENT_ATTN && d.la_rot_dim > 0))) {
+            RotaryDesc rdesc;
+            rdesc.dims = d.rot_dims; rdesc.base = d.rot_base; rdesc.factor = d.rot_factor; rdesc.original = d.rot_original; rdesc.fast = d.rot_fast;
+            rdesc.slow = d.rot_slow;
+            B2_TRY(S.rot_tab.alloc(Smax * (d.rot_dims / 2) * sizeof(float2)));
+            B2_TRY(rotary_table_build(rdesc, (int)Smax, S.rot_tab.as<float2>()));
+        }
+        if (d.type == B2_MIXER_GQA_ATTN) {
+            B2_TRY(S.kc.alloc(B * d.ga_kv_heads * Smax * d.ga_dim * F4));
+            B2_TRY(S.vc.alloc(B * d.ga_kv_heads * Smax * d.ga_vdim * F4));
+            cudaMemset(S.kc.p, 0, S.kc.bytes);
+            cudaMemset(S.vc.p, 0, S.vc.bytes);
+            if (d.ga_conv > 1) {
+                B2_TRY(S.conv_tail.alloc(B * (d.ga_conv - 1) * L.conv_ch * F4));
+                cudaMemset(S.conv_tail.p, 0, S.conv_tail.bytes);
+            }
+            if (d.ga_rot_values) {   // values turn over all of vdim with the plain frequencies of the same base
+                RotaryDesc vdesc;
+                vdesc.dims = d.ga_vdim; vdesc.base = d.rot_base;
+                B2_TRY(S.vrot_tab.alloc(Smax * (d.ga_vdim / 2) * sizeof(float2)));
+                B2_TRY(rotary_table_build(vdesc, (int)Smax, S.vrot_tab.as<float2>()));
+            }
+            maxH = std::max(maxH, d.ga_heads);
+            maxdv = std::max(maxdv, d.ga_vdim);
+        } else if (d.type == B2_MIXER_LATENT_ATTN) {
+            if (d.la_kv_from == 0) {   // a borrowing layer reads the owner's rows
+                B2_TRY(S.lat.alloc(B * Smax * L.lrow * F4));
+                cudaMemset(S.lat.p, 0, S.lat.bytes);
+            }
             maxH = std::max(maxH, d.la_heads);
             maxdv = std::max(maxdv, d.la_rank);
         } else if (d.type == B2_MIXER_HGRN2) {
@@ -894,7 +1192,7 @@ int seq_kv_alloc(b2_kv* kv) {
     }
     int kw = 0, vw = 0;
     for (const SeqLayerInfo& L : s.layers)
-        if (L.d.type == B2_MIXER_LATENT_ATTN) { kw = std::max(kw, (L.pq + 7) / 8 * 8); vw = std::max(vw, (L.pv + 7) / 8 * 8); }
+        if (L.d.type == B2_MIXER_LATENT_ATTN) { kw = std::max(kw, L.lqw_ld); vw = std::max(vw, (L.pv + 7) / 8 * 8); }
     if (kw > 0) {
         kv->seq->kmat_ld = kw; kv->seq->vmat_ld = vw;
         B2_TRY(kv->seq->kmat.alloc(Smax * kw * F4));
@@ -908,7 +1206,7 @@ int seq_kv_alloc(b2_kv* kv) {
 void seq_kv_free(b2_kv* kv) {
     if (kv->seq == nullptr) return;
     for (SeqLayerState& S : kv->seq->layer) {
-        DevBuf* bs[] = {&S.ssm, &S.conv_tail, &S.kc, &S.vc, &S.bucket_of, &S.wkv, &S.prev, &S.lat, &S.gla};
+        DevBuf* bs[] = {&S.ssm, &S.conv_tail, &S.kc, &S.vc, &S.bucket_of, &S.wkv, &S.prev, &S.lat, &S.gla, &S.canon1, &S.canon2, &S.rot_tab, &S.vrot_tab};
         for (DevBuf* b : bs) b->free();
     }
     kv->seq->last_tok.free();
@@ -935,7 +1233,9 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
     B2_CHECK_ARG(d.compute == B2_COMPUTE_BF16 || d.compute == B2_COMPUTE_F32, "b2_seq_model_create: unknown compute mode %d", d.compute);
     B2_CHECK_ARG(d.max_batch >= 1 && d.max_rows >= 1, "b2_seq_model_create: bad workspace sizing");
     B2_CHECK_ARG(d.norm_eps >= 0.f, "b2_seq_model_create: negative eps");
-    B2_CHECK_ARG(d.block == B2_BLOCK_POST_LN || d.block == B2_BLOCK_PRE_RMS1, "b2_seq_model_create: unknown block form %d", d.block);
+    B2_CHECK_ARG(d.block == B2_BLOCK_POST_LN || d.block == B2_BLOCK_PRE_RMS1 || d.block == B2_BLOCK_SANDWICH_RMS, "b2_seq_model_create: unknown block form %d", d.block);
+    B2_CHECK_ARG(d.input_conv_taps >= 0 && d.input_conv_taps <= 16, "b2_seq_model_create: 0..16 taps of the input convolution");
+    B2_CHECK_ARG(d.input_conv_taps <= 1 || d.block == B2_BLOCK_SANDWICH_RMS, "b2_seq_model_create: the input convolution belongs to the sandwich block");
     B2_CHECK_ARG(d.bigram_buckets >= 0 && d.logit_softcap >= 0.f, "b2_seq_model_create: negative bigram buckets or soft-cap");
     SeqModel* s = new SeqModel();
     s->d = d;
@@ -984,10 +1284,40 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             L.rn = l.r_heads * l.r_dim;
         } else if (l.type == B2_MIXER_LATENT_ATTN) {
             if (l.la_heads < 1 || l.la_dim < 1 || l.la_vdim < 1) why = "latent attention: heads and head sizes must be positive";
-            else if (l.la_rank < 1 || l.la_rank > 512) why = "latent attention: latent size 1..512";
-            L.pq = l.la_heads * l.la_dim; L.pv = l.la_heads * l.la_vdim;
-            L.pproj = L.pq + l.la_rank + l.la_heads;
+            else if (l.la_rot_dim < 0 || l.la_q_rank < 0 || l.la_kv_from < 0) why = "latent attention: negative size";
+            else if (l.la_rank < 1 || l.la_rank + l.la_rot_dim > 512) why = "latent attention: latent size + rotated part 1..512";
+            else if (l.la_rot_dim > 0 && (l.rot_dims < 2 || l.rot_dims % 2 || l.rot_dims > l.la_rot_dim || !(l.rot_base > 0.f))) why = "latent attention: an even number of rotated dimensions within the rotated part, positive base";
+            else if (l.rot_factor > 0.f && !(l.rot_original > 0.f && l.rot_fast > 0.f && l.rot_slow > 0.f && l.rot_base > 1.f)) why = "rotation: scaled frequencies need original, fast and slow";
+            else if (l.la_kv_from > 0) {
+                const int j = l.la_kv_from - 1;
+                if (j >= i) why = "latent attention: cache rows can only be read from an earlier layer";
+                else {
+                    const b2_seq_layer_desc& o = s->layers[j].d;
+                    if (o.type != B2_MIXER_LATENT_ATTN || o.la_kv_from != 0) why = "latent attention: the layer named by kv_from has no cache rows of its own";
+                    else if (o.la_rank != l.la_rank || o.la_rot_dim != l.la_rot_dim || o.rot_dims != l.rot_dims || o.rot_base != l.rot_base || o.rot_factor != l.rot_factor ||
+                             o.rot_original != l.rot_original || o.rot_fast != l.rot_fast || o.rot_slow != l.rot_slow)
+                        why = "latent attention: a layer that reads another's cache rows must have its latent size and rotation";
+                }
+            }
+            if (why == nullptr && (l.mask_kind < B2_MASK_CAUSAL || l.mask_kind > B2_MASK_CHUNK || (l.mask_kind != B2_MASK_CAUSAL && l.mask_size < 1))) why = "mask: unknown kind or empty size";
+            L.lrow = l.la_rank + l.la_rot_dim;
+            L.lqw = l.la_heads * (l.la_dim + l.la_rot_dim); L.lqw_ld = (L.lqw + 7) / 8 * 8;
+            L.pq = l.la_q_rank > 0 ? l.la_q_rank : L.lqw;   // rows of the query part of the fused projection
+            L.pv = l.la_heads * l.la_vdim;
+            L.pproj = L.pq + (l.la_kv_from == 0 ? L.lrow : 0) + (l.la_no_gate ? 0 : l.la_heads);
             L.pproj_ld = (L.pproj + 7) / 8 * 8;
+        } else if (l.type == B2_MIXER_GQA_ATTN) {
+            if (l.ga_heads < 1 || l.ga_kv_heads < 1 || l.ga_heads % l.ga_kv_heads) why = "attention: heads must be a positive multiple of kv_heads";
+            else if (l.ga_dim < 1 || l.ga_dim > 512 || l.ga_vdim < 1 || l.ga_vdim > 512) why = "attention: head sizes 1..512";
+            else if (l.ga_conv < 0 || l.ga_conv > 16) why = "attention: 0..16 convolution taps";
+            else if (l.rot_dims < 0 || l.rot_dims % 2 || l.rot_dims > l.ga_dim || (l.rot_dims > 0 && !(l.rot_base > 0.f))) why = "attention: an even number of rotated dimensions within a head, positive base";
+            else if (l.rot_factor > 0.f && !(l.rot_original > 0.f && l.rot_fast > 0.f && l.rot_slow > 0.f && l.rot_base > 1.f)) why = "rotation: scaled frequencies need original, fast and slow";
+            else if (l.ga_rot_values && (l.ga_vdim % 2 || !(l.rot_base > 0.f))) why = "attention: rotated values need an even vdim and a base";
+            else if (l.mask_kind < B2_MASK_CAUSAL || l.mask_kind > B2_MASK_CHUNK || (l.mask_kind != B2_MASK_CAUSAL && l.mask_size < 1)) why = "mask: unknown kind or empty size";
+            L.nq = l.ga_heads * l.ga_dim; L.nk = l.ga_kv_heads * l.ga_dim; L.nv = l.ga_kv_heads * l.ga_vdim; L.ng = l.ga_heads * l.ga_vdim;
+            L.lproj = L.nq + L.nk + L.nv + L.ng;
+            L.lproj_ld = (L.lproj + 7) / 8 * 8;
+            L.conv_ch = L.nq + L.nk + L.nv;
         } else if (l.type == B2_MIXER_HGRN2) {
             if (l.g_heads < 1 || l.g_dim < 1 || l.g_dim > 256 || l.g_vdim < 1) why = "hgrn2: heads, dim 1..256, vdim";
             L.pq = l.g_heads * l.g_dim; L.pv = l.g_heads * l.g_vdim;
@@ -996,14 +1326,15 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
         } else {
             why = "unknown mixer type";
         }
-        const bool pre_mixer = l.type == B2_MIXER_LATENT_ATTN || l.type == B2_MIXER_HGRN2;
-        if (why == nullptr && pre_mixer != (d.block == B2_BLOCK_PRE_RMS1)) why = "this mixer does not go with the model's block form";
+        const bool pre_mixer = l.type == B2_MIXER_LATENT_ATTN || l.type == B2_MIXER_HGRN2 || l.type == B2_MIXER_GQA_ATTN;
+        if (why == nullptr && pre_mixer != (d.block == B2_BLOCK_PRE_RMS1 || d.block == B2_BLOCK_SANDWICH_RMS)) why = "this mixer does not go with the model's block form";
         if (why == nullptr && l.ff > 0) {
-            if (l.ff_kind != B2_FF_RELU_SQ && d.block != B2_BLOCK_PRE_RMS1) why = "this feed-forward needs the pre-norm block";
+            if (l.ff_kind != B2_FF_RELU_SQ && d.block == B2_BLOCK_POST_LN) why = "this feed-forward needs a pre-norm or sandwich block";
             else if (l.ff_kind == B2_FF_MOE) {
                 if (l.moe_experts < 1 || l.moe_top < 1 || l.moe_top > 32 || l.moe_top > l.moe_experts) why = "moe: experts >= top >= 1, at most 32 choices";
                 else if (l.moe_groups < 1 || l.moe_experts % l.moe_groups || l.moe_keep < 1 || l.moe_keep > l.moe_groups) why = "moe: groups must divide experts, 1 <= keep <= groups";
                 else if (l.moe_shared_ff < 0) why = "moe: negative shared width";
+                else if (l.moe_score < 0 || l.moe_score > 1 || l.moe_group_score < 0 || l.moe_group_score > 1 || l.moe_act < 0 || l.moe_act > 1) why = "moe: unknown score, group score or activation";
             } else if (l.ff_kind != B2_FF_RELU_SQ && l.ff_kind != B2_FF_POLYNORM) why = "unknown feed-forward kind";
         }
         if (why == nullptr && L.src != i) {
@@ -1028,10 +1359,22 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
         for (int i = 0; i < d.n_layers; ++i) {
             if (looped && i == d.loop_start) {
                 for (int t = 0; t < d.loop_times; ++t)
-                    for (int j = d.loop_start; j < d.loop_stop; ++j) s->runs.push_back(SeqRun{j, j == d.loop_start ? t : -1});
+                    for (int j = d.loop_start; j < d.loop_stop; ++j) s->runs.push_back(SeqRun{j, j == d.loop_start ? t : -1, -1});
                 i = d.loop_stop - 1;
             } else {
-                s->runs.push_back(SeqRun{i, -1});
+                s->runs.push_back(SeqRun{i, -1, -1});
+            }
+        }
+        // a layer that reads another layer's cache rows reads those of that layer's latest run in front of it
+        for (size_t r = 0; r < s->runs.size(); ++r) {
+            const b2_seq_layer_desc& l = s->layers[s->runs[r].layer].d;
+            if (l.type != B2_MIXER_LATENT_ATTN || l.la_kv_from == 0) continue;
+            for (size_t q = r; q-- > 0;)
+                if (s->runs[q].layer == l.la_kv_from - 1) { s->runs[r].kv_run = (int)q; break; }
+            if (s->runs[r].kv_run < 0) {
+                set_error("b2_seq_model_create: layer %d runs before the layer whose cache rows it reads", s->runs[r].layer);
+                delete s;
+                return -1;
             }
         }
     }

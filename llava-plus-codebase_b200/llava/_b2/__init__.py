@@ -66,7 +66,15 @@ class SeqLayerDesc(_c.Structure):
                 ("ff_kind", _c.c_int32), ("moe_experts", _c.c_int32), ("moe_top", _c.c_int32), ("moe_groups", _c.c_int32),
                 ("moe_keep", _c.c_int32), ("moe_shared_ff", _c.c_int32), ("moe_scale", _c.c_float),
                 ("la_heads", _c.c_int32), ("la_dim", _c.c_int32), ("la_vdim", _c.c_int32), ("la_rank", _c.c_int32), ("la_scale", _c.c_float),
-                ("g_heads", _c.c_int32), ("g_dim", _c.c_int32), ("g_vdim", _c.c_int32)]
+                ("g_heads", _c.c_int32), ("g_dim", _c.c_int32), ("g_vdim", _c.c_int32),
+                ("moe_score", _c.c_int32), ("moe_group_score", _c.c_int32), ("moe_raw_weights", _c.c_int32), ("moe_act", _c.c_int32),
+                ("la_q_rank", _c.c_int32), ("la_rot_dim", _c.c_int32), ("la_no_sink", _c.c_int32), ("la_no_gate", _c.c_int32),
+                ("la_kv_from", _c.c_int32),
+                ("ga_heads", _c.c_int32), ("ga_kv_heads", _c.c_int32), ("ga_dim", _c.c_int32), ("ga_vdim", _c.c_int32), ("ga_conv", _c.c_int32),
+                ("ga_rot_values", _c.c_int32), ("ga_sink", _c.c_int32), ("ga_scale", _c.c_float), ("ga_sink_value", _c.c_float),
+                ("mask_kind", _c.c_int32), ("mask_size", _c.c_int32), ("rot_dims", _c.c_int32),
+                ("rot_base", _c.c_float), ("rot_factor", _c.c_float), ("rot_original", _c.c_float), ("rot_fast", _c.c_float),
+                ("rot_slow", _c.c_float)]
 
 
 class SeqModelDesc(_c.Structure):
@@ -75,12 +83,17 @@ class SeqModelDesc(_c.Structure):
                 ("norm_eps", _c.c_float), ("max_batch", _c.c_int32), ("max_rows", _c.c_int32),
                 ("block", _c.c_int32), ("residual_mult", _c.c_float), ("logit_softcap", _c.c_float),
                 ("bigram_buckets", _c.c_int32), ("bigram_mul_prev", _c.c_int32), ("bigram_mul_cur", _c.c_int32),
-                ("loop_start", _c.c_int32), ("loop_stop", _c.c_int32), ("loop_times", _c.c_int32)]
+                ("loop_start", _c.c_int32), ("loop_stop", _c.c_int32), ("loop_times", _c.c_int32),
+                ("logit_scale", _c.c_float), ("input_conv_taps", _c.c_int32)]
 
 
-MIXER_MAMBA2, MIXER_PARALLEL, MIXER_LATENT_ATTN, MIXER_HGRN2 = 1, 2, 3, 4
+MIXER_MAMBA2, MIXER_PARALLEL, MIXER_LATENT_ATTN, MIXER_HGRN2, MIXER_GQA_ATTN = 1, 2, 3, 4, 5
 FF_RELU_SQ, FF_POLYNORM, FF_MOE = 0, 1, 2
-BLOCK_POST_LN, BLOCK_PRE_RMS1 = 0, 1
+BLOCK_POST_LN, BLOCK_PRE_RMS1, BLOCK_SANDWICH_RMS = 0, 1, 2
+MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
+MOE_SCORE_SIGMOID, MOE_SCORE_SOFTMAX = 0, 1
+MOE_GROUP_TOP2_SUM, MOE_GROUP_MAX = 0, 1
+MOE_ACT_SWIGLU, MOE_ACT_RELU_SQ = 0, 1
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
 
 

@@ -11,12 +11,15 @@ MODEL_REGISTRY = {
     "llava": ("language_model.llava_llama", "LlavaLlamaForCausalLM"),
     "Katadra": ("language_model.katadra", "KatadraForCausalLM"),
     "Pefivik": ("language_model.pefivik", "PefivikForCausalLM"),
+    "Fezuzen": ("language_model.fezuzen", "FezuzenForCausalLM"),
 }
 _LAZY = {"LlavaLlamaForCausalLM": "language_model.llava_llama", "LlavaConfig": "language_model.llava_llama",
          "KatadraForCausalLM": "language_model.katadra", "KatadraConfig": "language_model.katadra",
-         "PefivikForCausalLM": "language_model.pefivik", "PefivikConfig": "language_model.pefivik"}
+         "PefivikForCausalLM": "language_model.pefivik", "PefivikConfig": "language_model.pefivik",
+         "FezuzenForCausalLM": "language_model.fezuzen", "FezuzenConfig": "language_model.fezuzen"}
 
-__all__ = ["LlavaConfig", "LlavaLlamaForCausalLM", "KatadraConfig", "KatadraForCausalLM", "PefivikConfig", "PefivikForCausalLM", "MODEL_REGISTRY",
+__all__ = ["LlavaConfig", "LlavaLlamaForCausalLM", "KatadraConfig", "KatadraForCausalLM", "PefivikConfig", "PefivikForCausalLM", "FezuzenConfig",
+           "FezuzenForCausalLM", "MODEL_REGISTRY",
            "model_class_for"]
 
 
