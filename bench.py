@@ -55,11 +55,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the side measurements of the other BASELINE configs")
-    ap.add_argument("--arch", default="llava", choices=["llava", "katadra", "pefivik"],
+    ap.add_argument("--arch", default="llava", choices=["llava", "katadra", "pefivik", "fezuzen"],
                     help="katadra: prefill / decode throughput of the layer-list decoder beside the LLaMA decoder of equal width, "
                          "depth and parameter count (random weights); the default workload and its JSON line are unchanged")
-    ap.add_argument("--widths", default="2048,4096", help="--arch katadra / pefivik: model widths to measure")
-    ap.add_argument("--ctx", type=int, default=2048, help="--arch katadra / pefivik: prompt length")
+    ap.add_argument("--widths", default="2048,4096", help="--arch katadra / pefivik / fezuzen: model widths to measure")
+    ap.add_argument("--ctx", type=int, default=2048, help="--arch katadra / pefivik / fezuzen: prompt length")
     return ap.parse_args()
 
 
@@ -876,6 +876,82 @@ def run_pefivik(args):
     print(json.dumps(out))
 
 
+def fezuzen_config(width, ctx):
+    """Four layers of the sizes a model of this width would have: latent attention (heads of 128 + 64 rotated, latent 512, queries
+    through a latent of 3/4 width, a window of half the prompt; the third layer reads the first one's cache rows) and grouped
+    attention (heads of 128, four query heads per key/value head, 4-tap convolutions, chunks of half the prompt), each with a
+    16-expert mixture (top 2 of the best 2 of 4 groups, expert width width / 2, a shared expert of width) behind 4-tap input
+    convolutions."""
+    heads = width // 128
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 3 * width // 4,
+                                                 "mask": {"size": ctx // 2}, "rot": rot, "scale": 192 ** -0.5}}
+    gqa = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4, "mask": {"size": ctx // 2},
+                                          "rot": {"base": 1.0e6, "dims": 128}, "scale": 128 ** -0.5}}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "shared": {"ff": width}, "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    lat2 = {"type": "latent_attention", "mixer": dict(lat["mixer"], kv_from=0)}
+    return {"architecture": "Fezuzen", "width": width, "vocab": 32000, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "logit_scale": 0.5,
+            "layers": [dict(lat, mlp=moe), dict(gqa, mlp=moe), dict(lat2, mlp=moe), dict(gqa, mlp=moe)]}
+
+
+def fezuzen_params(cfg):
+    """(matmul parameters a token multiplies with, function B -> parameters a decode step of B slots reads)"""
+    W = cfg["width"]
+    fixed, per_expert, experts, top = cfg["vocab"] * W, 0, 1, 0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "latent_attention":
+            H = m["heads"]
+            fixed += m["q_rank"] * W + H * (m["dim"] + m["rot_dim"]) * m["q_rank"] + H * (m["dim"] + m["vdim"]) * m["kv_rank"] + W * H * m["vdim"]
+            if m.get("kv_from") is None:
+                fixed += (m["kv_rank"] + m["rot_dim"]) * W
+        else:
+            H, G = m["heads"], m["kv_heads"]
+            fixed += (H * m["dim"] + G * m["dim"] + G * m["vdim"] + 2 * H * m["vdim"]) * W
+        mlp = layer["mlp"]
+        r = mlp["router"]
+        experts, top = r["experts"], r["top"]
+        fixed += r["experts"] * W + 2 * mlp["shared"]["ff"] * W
+        per_expert += 2 * mlp["expert"]["ff"] * W
+    return fixed + top * per_expert, lambda B: fixed + per_expert * experts * (1.0 - (1.0 - top / experts) ** B)
+
+
+def run_fezuzen(args):
+    """Fezuzen beside Pefivik, the package's closest model (latent attention, mixture of experts), at equal width and depth."""
+    from oracle import fezuzen_oracle as FO
+    from oracle import pefivik_oracle as PO
+    from llava.model import FezuzenConfig, FezuzenForCausalLM, PefivikConfig, PefivikForCausalLM
+    from llava._b2 import launch_count
+
+    dev = torch.device("cuda:0")
+    hbm, tfl, src = peaks()
+    pk = {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}
+    S, N, layers = args.ctx, 64, 4
+    flush = torch.zeros(160 * 1024 * 1024 // 4, device=dev)  # 160 MB > 126 MB of L2
+    out = {"metric": "Fezuzen vs Pefivik (layer-list decoders) at equal width and depth", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+           "peaks": pk, "prompt": S, "decode_steps": N, "l2": "160 MB written before every timed run", "sizes": []}
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    for width in [int(w) for w in args.widths.split(",")]:
+        row = {"width": width, "layers": layers}
+        for name, mk_cfg, mk_params, oracle, cfg_cls, model_cls in (("fezuzen", lambda: fezuzen_config(width, S), fezuzen_params, FO, FezuzenConfig, FezuzenForCausalLM),
+                                                                    ("pefivik", lambda: pefivik_config(width), pefivik_params, PO, PefivikConfig, PefivikForCausalLM)):
+            cfg = mk_cfg()
+            w = oracle.random_weights(cfg, seed=0)
+            params, params_read = mk_params(cfg)
+            model = model_cls(cfg_cls(**cfg), {k: torch.from_numpy(np.asarray(v, np.float32)).bfloat16() for k, v in w.items()}, device=dev, dtype=torch.bfloat16,
+                              max_batch=8, max_seq=S + N + 8, max_rows=S)
+            row[name + "_params_total"] = int(sum(v.size for k, v in w.items() if v.ndim == 2 and k not in ("embed", "bigram", "loop.step")))
+            del w
+            row[name] = measure_layer_list(model, args, S, N, flush, pk, params, params_read)
+            del model
+        out["sizes"].append(row)
+    out["clocks"] = sampler.stop()
+    out["gpu_launches"] = launch_count() - launches0
+    print(json.dumps(out))
+
+
 def run_katadra(args):
     from oracle import katadra_oracle as KO
     from llava.model import KatadraConfig, KatadraForCausalLM
@@ -936,10 +1012,10 @@ def run_katadra(args):
 
 def main():
     args = parse_args()
-    if args.arch in ("katadra", "pefivik"):
+    if args.arch in ("katadra", "pefivik", "fezuzen"):
         if not torch.cuda.is_available():
             raise RuntimeError(f"bench.py --arch {args.arch} needs a B200")
-        return run_katadra(args) if args.arch == "katadra" else run_pefivik(args)
+        return {"katadra": run_katadra, "pefivik": run_pefivik, "fezuzen": run_fezuzen}[args.arch](args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -39,8 +39,8 @@ def causal_conv(u, taps_w):
 
 
 def input_conv(h, taps_w):
-    """What a sublayer reads: its input plus the causal convolution of its input."""
-    return h + causal_conv(h, taps_w)
+    """What a sublayer reads: its input plus the causal convolution of its input (taps_w None: the input itself)."""
+    return h if taps_w is None else h + causal_conv(h, taps_w)
 
 
 # ------------------------------------------------------------------------------------------------- rotations
@@ -80,11 +80,22 @@ def visible(i, j, kind, size):
     """Whether position i sees position j <= i: a sliding window of `size` positions, or chunks of `size` counted from 0."""
     if j > i:
         return False
+    if size is None:
+        return True
     if kind == "window":
         return i - j < size
-    if kind == "chunk":
-        return i // size == j // size
-    return True
+    return i // size == j // size
+
+
+def visible_keys(i, kind, size):
+    """Positions that position i sees (under either mask nothing further back than `size` positions can be visible)."""
+    first = 0 if size is None else max(0, i - size)
+    return [j for j in range(first, i + 1) if visible(i, j, kind, size)]
+
+
+def mask_size(mix):
+    m = mix.get("mask")
+    return int(m["size"]) if m and m.get("size") is not None else None
 
 
 def latent_kv(h, p, mix, eps):
@@ -103,7 +114,7 @@ def latent_attention(h, p, mix, eps, kv=None):
     queries through a latent of their own; sliding window; ordinary softmax. kv: (c, kr) of the layer it borrows them from."""
     T = h.shape[0]
     H, dk, rd, dv = int(mix["heads"]), int(mix["dim"]), int(mix["rot_dim"]), int(mix["vdim"])
-    scale, size = float(mix["scale"]), int(mix["mask"]["size"])
+    scale, size = float(mix["scale"]), mask_size(mix)
     freq, mag = rotary_frequencies(mix["rot"])
     cq = rms_norm(h @ p["dq"].T, p["dq.norm"], eps)
     q = (cq @ p["uq"].T).reshape(T, H, dk + rd)
@@ -112,42 +123,41 @@ def latent_attention(h, p, mix, eps, kv=None):
     v = (c @ p["uv"].T).reshape(T, H, dv)
     out = np.zeros((T, H, dv), F)
     for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, "window", size)]
+        js = visible_keys(i, "window", size)
         for hd in range(H):
             qn, qr = q[i, hd, :dk], rotate_pairs(q[i, hd, dk:], i, freq, mag)
-            s = np.array([(qn @ k[j, hd] + qr @ kr[j]) * scale for j in js], F)
+            s = (k[js, hd] @ qn + kr[js] @ qr) * scale
             e = np.exp(s - s.max())
-            wgt = e / e.sum()
-            out[i, hd] = sum(wgt[n] * v[j, hd] for n, j in enumerate(js))
+            out[i, hd] = (e / e.sum()) @ v[js, hd]
     return out.reshape(T, H * dv) @ p["o"].T
 
 
-def grouped_attention(h, p, mix):
+def grouped_attention(h, p, mix, extra_one=True):
     """Attention with grouped key/value heads: short convolutions on q, k, v; rotary q, k; values rotated by their own position
-    and the head's output turned back by the query's; chunked mask; a softmax whose denominator holds one extra 1; sigmoid
-    output gate."""
+    and the head's output turned back by the query's; chunked mask; a softmax whose denominator holds one extra 1 (extra_one False
+    leaves it out: what a test compares with to see that the term matters); sigmoid output gate."""
     T = h.shape[0]
     H, G, dk, dv = int(mix["heads"]), int(mix["kv_heads"]), int(mix["dim"]), int(mix["vdim"])
-    scale, size = float(mix["scale"]), int(mix["mask"]["size"])
+    scale, size = float(mix["scale"]), mask_size(mix)
     freq, mag = rotary_frequencies(mix["rot"])
     vfreq = np.array([float(mix["rot"]["base"]) ** (-2.0 * m / dv) for m in range(dv // 2)], F)
-    q = causal_conv(h @ p["q"].T, p["q.conv"]).reshape(T, H, dk)
-    k = causal_conv(h @ p["k"].T, p["k.conv"]).reshape(T, G, dk)
-    v = causal_conv(h @ p["v"].T, p["v.conv"]).reshape(T, G, dv)
+    conv = (lambda u, n: causal_conv(u, p[n + ".conv"])) if int(mix.get("conv", 0) or 0) > 1 else (lambda u, n: u)
+    q = conv(h @ p["q"].T, "q").reshape(T, H, dk)
+    k = conv(h @ p["k"].T, "k").reshape(T, G, dk)
+    v = conv(h @ p["v"].T, "v").reshape(T, G, dv)
     gate = sigmoid(h @ p["g"].T).reshape(T, H, dv)
     q = np.stack([rotate_pairs(q[t], t, freq, mag) for t in range(T)])
     k = np.stack([rotate_pairs(k[t], t, freq, mag) for t in range(T)])
     v = np.stack([rotate_pairs(v[t], t, vfreq) for t in range(T)])
     out = np.zeros((T, H, dv), F)
     for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, "chunk", size)]
+        js = visible_keys(i, "chunk", size)
         for hd in range(H):
             g = hd // (H // G)
-            s = np.array([(q[i, hd] @ k[j, g]) * scale for j in js], F)
+            s = (k[js, g] @ q[i, hd]) * scale
             m = max(s.max(), 0.0)
             e = np.exp(s - m)
-            wgt = e / (math.exp(-m) + e.sum())
-            o = sum(wgt[n] * v[j, g] for n, j in enumerate(js))
+            o = (e / ((math.exp(-m) if extra_one else 0.0) + e.sum())) @ v[js, g]
             out[i, hd] = rotate_pairs(o, -i, vfreq) * gate[i, hd]
     return out.reshape(T, H * dv) @ p["o"].T
 
@@ -204,7 +214,7 @@ def forward(cfg, w, tokens, return_layers=False):
     kept, per_layer = {}, []
     for i, layer in enumerate(cfg["layers"]):
         mix, mlp = layer["mixer"], layer.get("mlp")
-        g = lambda n: np.asarray(w[f"l{i}.{n}"], F)
+        g = lambda n: np.asarray(w[f"l{i}.{n}"], F) if f"l{i}.{n}" in w else None  # noqa: E731
         h = input_conv(rms_norm(x, g("norm1"), eps), g("canon1"))
         p = layer_params(w, i, "mix")
         if layer["type"] == "latent_attention":
@@ -236,13 +246,14 @@ def bf16_round(a):
 
 def tensor_shapes(cfg):
     """name -> shape of every tensor a checkpoint of this configuration holds."""
-    width, vocab, ct = int(cfg["width"]), int(cfg["vocab"]), int(cfg["canon"]["taps"])
+    width, vocab, ct = int(cfg["width"]), int(cfg["vocab"]), int((cfg.get("canon") or {}).get("taps", 0))
     out = {"embed": (vocab, width), "head": (vocab, width), "final.norm": (width,)}
     for i, layer in enumerate(cfg["layers"]):
         mix, mlp = layer["mixer"], layer.get("mlp")
         a = f"l{i}."
         out[a + "norm1"] = out[a + "norm1b"] = (width,)
-        out[a + "canon1"] = (width, ct)
+        if ct > 1:
+            out[a + "canon1"] = (width, ct)
         if layer["type"] == "latent_attention":
             H, dk, rd, dv, rank, qr = (int(mix[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"))
             out[a + "mix.dq"], out[a + "mix.dq.norm"], out[a + "mix.uq"] = (qr, width), (qr,), (H * (dk + rd), qr)
@@ -250,13 +261,17 @@ def tensor_shapes(cfg):
                 out[a + "mix.dkv"], out[a + "mix.dkv.norm"] = (rank + rd, width), (rank,)
             out[a + "mix.uk"], out[a + "mix.uv"], out[a + "mix.o"] = (H * dk, rank), (H * dv, rank), (width, H * dv)
         else:
-            H, G, dk, dv, taps = (int(mix[k]) for k in ("heads", "kv_heads", "dim", "vdim", "conv"))
+            H, G, dk, dv = (int(mix[k]) for k in ("heads", "kv_heads", "dim", "vdim"))
+            taps = int(mix.get("conv", 0) or 0)
             for n, rows in (("q", H * dk), ("k", G * dk), ("v", G * dv)):
-                out[a + "mix." + n], out[a + "mix." + n + ".conv"] = (rows, width), (rows, taps)
+                out[a + "mix." + n] = (rows, width)
+                if taps > 1:
+                    out[a + "mix." + n + ".conv"] = (rows, taps)
             out[a + "mix.g"], out[a + "mix.o"] = (H * dv, width), (width, H * dv)
         if mlp:
             out[a + "norm2"] = out[a + "norm2b"] = (width,)
-            out[a + "canon2"] = (width, ct)
+            if ct > 1:
+                out[a + "canon2"] = (width, ct)
             ff = int(mlp["expert"]["ff"])
             out[a + "mlp.router"] = (int(mlp["router"]["experts"]), width)
             for e in range(int(mlp["router"]["experts"])):
