@@ -402,7 +402,7 @@ __global__ void __launch_bounds__(512) attn_merge_kernel(BiasAttnArgs a) {
 int check_args(const BiasAttnArgs& a, const char* who) {
     B2_CHECK_ARG(a.q && a.kcache && a.vcache && a.row_slot && a.row_pos && a.rows > 0, "%s: null argument", who);
     B2_CHECK_ARG(a.H > 0 && a.G > 0 && a.H % a.G == 0, "%s: %d query heads cannot share %d key/value heads", who, a.H, a.G);
-    B2_CHECK_ARG(a.dk > 0 && a.dk <= 512 && a.dv > 0 && a.dv <= 512, "%s: head sizes %d / %d exceed 512", who, a.dk, a.dv);
+    B2_CHECK_ARG(a.dk > 0 && a.dk <= 768 && a.dv > 0 && a.dv <= 512, "%s: head sizes %d / %d exceed 768 / 512", who, a.dk, a.dv);
     B2_CHECK_ARG(a.vcache != a.kcache || a.dv <= a.dk, "%s: keys that also hold the values need dv <= dk", who);
     B2_CHECK_ARG(a.mask_kind == MASK_CAUSAL || ((a.mask_kind == MASK_WINDOW || a.mask_kind == MASK_CHUNK) && a.mask_size >= 1), "%s: mask %d of size %d", who, a.mask_kind, a.mask_size);
     B2_CHECK_ARG(a.kv_row_stride == 0 || (a.kv_row_stride_v > 0 && a.tile_rows >= 1 && a.vcache != a.kcache), "%s: key/value matrices need both pitches and the tiled kernel", who);

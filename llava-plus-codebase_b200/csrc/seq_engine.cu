@@ -1285,7 +1285,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
         } else if (l.type == B2_MIXER_LATENT_ATTN) {
             if (l.la_heads < 1 || l.la_dim < 1 || l.la_vdim < 1) why = "latent attention: heads and head sizes must be positive";
             else if (l.la_rot_dim < 0 || l.la_q_rank < 0 || l.la_kv_from < 0) why = "latent attention: negative size";
-            else if (l.la_rank < 1 || l.la_rank + l.la_rot_dim > 512) why = "latent attention: latent size + rotated part 1..512";
+            else if (l.la_rank < 1 || l.la_rank > 512 || l.la_rank + l.la_rot_dim > 768) why = "latent attention: latent size 1..512, with the rotated part at most 768";
             else if (l.la_rot_dim > 0 && (l.rot_dims < 2 || l.rot_dims % 2 || l.rot_dims > l.la_rot_dim || !(l.rot_base > 0.f))) why = "latent attention: an even number of rotated dimensions within the rotated part, positive base";
             else if (l.rot_factor > 0.f && !(l.rot_original > 0.f && l.rot_fast > 0.f && l.rot_slow > 0.f && l.rot_base > 1.f)) why = "rotation: scaled frequencies need original, fast and slow";
             else if (l.la_kv_from > 0) {
