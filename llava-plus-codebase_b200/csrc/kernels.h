@@ -387,6 +387,20 @@ int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, f
 int rms_weight_f32(const float* in, int64_t ld_in, const int32_t* row_index, const float* w, float* out, int64_t ld_out, int accumulate, int rows,
                    int cols, float eps, cudaStream_t stream);
 
+// The norms around a sublayer of a sandwich block in one pass over a row: first (y, w_post non-null) x += rms_w_post(y), the normed
+// output of the previous sublayer joining the residual stream; then (w_pre non-null) out = rms_w_pre(x), the next sublayer's input.
+// With conv_w the input convolution of a decode step rides along: every row is a segment of ONE token (row r = segs[r]), conv_out =
+// out + sum_j conv_w[c, j] * (the taps - 1 carried inputs of the slot, then out itself), and the carried inputs move on by one
+// (a segment at position 0 starts from zeros; an idle segment, n == 0, is left alone).
+struct SandwichNormArgs {
+    const float* y = nullptr; const float* w_post = nullptr;
+    float* x = nullptr;
+    const float* w_pre = nullptr; float* out = nullptr;
+    const float* conv_w = nullptr; float* tail = nullptr; int taps = 0; const SeqSeg* segs = nullptr; float* conv_out = nullptr;
+    int rows = 0, cols = 0; float eps = 0.f;
+};
+int sandwich_norm_f32(const SandwichNormArgs& a, cudaStream_t stream);
+
 // ---- rotary positions (rotary.cu) -------------------------------------------------------------------------------------------
 // Pairs (2m, 2m+1), m < dims / 2, turn by position * f_m, f_m = base^(-2m / dims). factor > 0: f_m is blended towards f_m / factor
 // over the pairs between lo = max(floor(dim(fast)), 0) and hi = min(ceil(dim(slow)), dims - 1), dim(t) = dims ln(original / (2 pi t)) /
@@ -408,6 +422,8 @@ struct RotateArgs {
     const int32_t* row_slot = nullptr; const int32_t* row_pos = nullptr;
 };
 int rotate_rows_f32(const RotateArgs& a, cudaStream_t stream);
+// up to three such calls over the same rows in one launch (queries, keys and values of an attention layer)
+int rotate_rows_multi_f32(const RotateArgs* parts, int n, cudaStream_t stream);
 // Row of a low-rank key/value cache with a rotated key part: cache[slot][pos] = [unit_rms(in[r, :rank]) * gamma | the 2 * pairs entries
 // behind them turned by the row's position]; rows of the cache have rank + 2 * pairs entries
 int latent_rot_append_f32(const float* in, int64_t ld_in, const float* gamma, float* cache, const int32_t* row_slot, const int32_t* row_pos, int rows,

@@ -143,6 +143,134 @@ __global__ void rms_weight_kernel(const float* __restrict__ in, int64_t ld_in, c
     }
 }
 
+// post-norm add of one sublayer, pre-norm of the next, and (decode steps) the input convolution with its carried inputs
+__global__ void sandwich_norm_kernel(SandwichNormArgs a) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const int cols = a.cols;
+    float* xr = a.x + r * cols;
+    float q = 0.f;
+    if (a.y != nullptr) {
+        const float* yr = a.y + r * cols;
+        float qy = 0.f;
+#pragma unroll 4
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) qy = fmaf(yr[c], yr[c], qy);
+        const float mul = 1.f / sqrtf(block_sum(qy, red) / (float)cols + a.eps);
+#pragma unroll 4
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float v = fmaf(yr[c] * mul, a.w_post[c], xr[c]);
+            xr[c] = v;
+            q = fmaf(v, v, q);
+        }
+    } else {
+#pragma unroll 4
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) q = fmaf(xr[c], xr[c], q);
+    }
+    if (a.w_pre == nullptr) return;
+    const float mul = 1.f / sqrtf(block_sum(q, red) / (float)cols + a.eps);
+    float* o = a.out + r * cols;
+    if (a.conv_w == nullptr) {
+#pragma unroll 4
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) o[c] = xr[c] * mul * a.w_pre[c];
+        return;
+    }
+    const SeqSeg sg = a.segs[r];
+    const int taps = a.taps;
+    float* tl = a.tail + (size_t)sg.slot * (taps - 1) * cols;
+    float* co = a.conv_out + r * cols;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = xr[c] * mul * a.w_pre[c];
+        o[c] = v;
+        if (sg.n <= 0) continue;
+        const float* wc = a.conv_w + (size_t)c * taps;
+        float acc = fmaf(wc[taps - 1], v, v);
+        for (int j = 0; j < taps - 1; ++j) {
+            const float old = sg.pos0 > 0 ? tl[(size_t)j * cols + c] : 0.f;
+            acc = fmaf(wc[j], old, acc);
+            if (j > 0) tl[(size_t)(j - 1) * cols + c] = old;
+        }
+        tl[(size_t)(taps - 2) * cols + c] = v;
+        co[c] = acc;
+    }
+}
+
+// the same for rows of at most blockDim.x * V entries: a thread keeps its V entries in registers and the row is read once. Everything
+// the kernel will need (both weights, and with TP > 0 the up to TP carried inputs and TP + 1 taps of the fused convolution) is loaded
+// in front of the first reduction, so the launch costs one memory round trip and not one per pass (a decode step has ONE block per
+// row and is bound by round trips, not by bandwidth).
+template <int V, int TP>
+__global__ void __launch_bounds__(512) sandwich_norm_reg_kernel(SandwichNormArgs a) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const int cols = a.cols, tid = threadIdx.x, nt = blockDim.x;
+    float* xr = a.x + r * cols;
+    float xv[V], yv[V], wpost[V], wpre[V];
+    float old[TP > 0 ? TP : 1][V], cw[TP + 1][V];
+    const bool conv = TP > 0 && a.conv_w != nullptr;
+    const int taps = a.taps;
+    SeqSeg sg = {0, 0, 0, 0};
+    if (conv) sg = a.segs[r];
+    float* tl = conv ? a.tail + (size_t)sg.slot * (taps - 1) * cols : nullptr;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = tid + i * nt;
+        const bool ok = c < cols;
+        xv[i] = ok ? xr[c] : 0.f;
+        yv[i] = (ok && a.y != nullptr) ? a.y[r * cols + c] : 0.f;
+        wpost[i] = (ok && a.y != nullptr) ? a.w_post[c] : 0.f;
+        wpre[i] = (ok && a.w_pre != nullptr) ? a.w_pre[c] : 0.f;
+        if (TP > 0) {
+#pragma unroll
+            for (int j = 0; j < TP; ++j) {   // carried input j and tap j, right-aligned: entry TP - 1 is the newest carried input
+                const int tj = j - (TP - (taps - 1));
+                old[j][i] = (conv && ok && tj >= 0 && sg.pos0 > 0) ? tl[(size_t)tj * cols + c] : 0.f;
+                cw[j][i] = (conv && ok && tj >= 0) ? a.conv_w[(size_t)c * taps + tj] : 0.f;
+            }
+            cw[TP][i] = (conv && ok) ? a.conv_w[(size_t)c * taps + taps - 1] : 0.f;
+        }
+    }
+    if (a.y != nullptr) {
+        float qy = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) qy = fmaf(yv[i], yv[i], qy);
+        const float mul = 1.f / sqrtf(block_sum(qy, red) / (float)cols + a.eps);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int c = tid + i * nt;
+            xv[i] = fmaf(yv[i] * mul, wpost[i], xv[i]);
+            if (c < cols) xr[c] = xv[i];
+        }
+    }
+    if (a.w_pre == nullptr) return;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) q = fmaf(xv[i], xv[i], q);
+    const float mul = 1.f / sqrtf(block_sum(q, red) / (float)cols + a.eps);
+    float* o = a.out + r * cols;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = tid + i * nt;
+        xv[i] = xv[i] * mul * wpre[i];
+        if (c < cols) o[c] = xv[i];
+    }
+    if (!conv || sg.n <= 0) return;
+    float* co = a.conv_out + r * cols;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = tid + i * nt;
+        if (c >= cols) continue;
+        float acc = fmaf(cw[TP][i], xv[i], xv[i]);
+#pragma unroll
+        for (int j = 0; j < TP; ++j) {
+            acc = fmaf(cw[j][i], old[j][i], acc);
+            const int tj = j - (TP - (taps - 1));
+            if (tj >= 1) tl[(size_t)(tj - 1) * cols + c] = old[j][i];
+        }
+        tl[(size_t)(taps - 2) * cols + c] = xv[i];
+        co[c] = acc;
+    }
+}
+
 // dst[b][c][r] = src[b][r][c] for elements of 2 or 4 bytes
 template <typename T>
 __global__ void transpose_blocks_kernel(const T* __restrict__ src, T* __restrict__ dst, int rows, int cols) {
@@ -351,6 +479,23 @@ int rms_weight_f32(const float* in, int64_t ld_in, const int32_t* row_index, con
                    int cols, float eps, cudaStream_t st) {
     B2_CHECK_ARG(in && w && out && rows > 0 && cols > 0, "rms_weight: bad argument");
     rms_weight_kernel<<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(in, ld_in, row_index, w, out, ld_out, accumulate, cols, eps);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int sandwich_norm_f32(const SandwichNormArgs& a, cudaStream_t st) {
+    B2_CHECK_ARG(a.x && a.rows > 0 && a.cols > 0 && (a.y == nullptr) == (a.w_post == nullptr) && (a.w_pre == nullptr || a.out != nullptr), "sandwich_norm: bad argument");
+    B2_CHECK_ARG(a.conv_w == nullptr || (a.w_pre && a.tail && a.segs && a.conv_out && a.taps >= 2 && a.taps <= 16), "sandwich_norm: the fused convolution needs taps, tail and segments");
+    // rows of up to 4096 entries live in registers (4 entries per thread for narrow rows, 8 otherwise); the fused convolution rides in
+    // that kernel with up to 4 taps, and in the plain one otherwise
+    const bool conv = a.conv_w != nullptr;
+    if (a.cols <= 4096 && (!conv || a.taps <= 4)) {
+        const int t4 = (a.cols + 127) / 128 * 32, t8 = (a.cols + 255) / 256 * 32;
+        if (a.cols <= 512) { if (conv) sandwich_norm_reg_kernel<4, 3><<<a.rows, t4, 0, st>>>(a); else sandwich_norm_reg_kernel<4, 0><<<a.rows, t4, 0, st>>>(a); }
+        else { if (conv) sandwich_norm_reg_kernel<8, 3><<<a.rows, t8, 0, st>>>(a); else sandwich_norm_reg_kernel<8, 0><<<a.rows, t8, 0, st>>>(a); }
+    } else {
+        sandwich_norm_kernel<<<a.rows, 256, 0, st>>>(a);
+    }
     B2_LAUNCH_CHECK();
     return 0;
 }

@@ -19,11 +19,11 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 // call, or the carried tail for positions before the call) and walks the tile. The compute kernel only READS the tail; a
 // second small kernel replaces it afterwards, so tiles never race with the update.
 constexpr int CONV_MAX_TAPS = 16, CONV_TILE = 32;
-template <int FLAGS>   // CONV_SILU | CONV_ADD_INPUT
+template <int FLAGS>   // CONV_SILU | CONV_ADD_INPUT; own_tail: every segment is ONE tile, whose thread replaces the carried inputs itself
 __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ w,
-                                                          const float* __restrict__ bias, const float* __restrict__ tail,
+                                                          const float* __restrict__ bias, float* __restrict__ tail,
                                                           float* __restrict__ out, int64_t ld_out, int C, int taps,
-                                                          const SeqSeg* __restrict__ segs) {
+                                                          const SeqSeg* __restrict__ segs, int own_tail) {
     const SeqSeg sg = segs[blockIdx.z];
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int tt0 = blockIdx.y * CONV_TILE;
@@ -65,6 +65,14 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restric
                 if (FLAGS & CONV_ADD_INPUT) acc += v[u];
                 op[(size_t)(t0 + u) * ld_out] = (FLAGS & CONV_SILU) ? silu_f(acc) : acc;
             }
+        }
+    }
+    if (own_tail && taps > 1) {   // the window now ends with the segment's last input: its last taps - 1 entries are the new carried inputs
+        float* tw = tail + (size_t)sg.slot * (taps - 1) * C + c;
+#pragma unroll
+        for (int jp = 0; jp < CONV_MAX_TAPS; ++jp) {
+            const int j = jp - (CONV_MAX_TAPS - (taps - 1));
+            if (j >= 0) tw[(size_t)j * C] = win[jp];
         }
     }
 }
@@ -296,14 +304,15 @@ int causal_conv_f32(const float* in, int64_t ld_in, const float* w, const float*
     B2_CHECK_ARG(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: 1..%d taps are supported (got %d)", CONV_MAX_TAPS, taps);
     // the grid covers the longest segment the call may hold; tiles past a segment's end return at once
     const dim3 grid((C + 127) / 128, (max_n + CONV_TILE - 1) / CONV_TILE, nseg);
+    const int own = max_n <= CONV_TILE;   // one tile per segment (decode steps, short portions): no second kernel for the carried inputs
     switch (flags & (CONV_SILU | CONV_ADD_INPUT)) {
-        case 0: causal_conv_kernel<0><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
-        case CONV_SILU: causal_conv_kernel<CONV_SILU><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
-        case CONV_ADD_INPUT: causal_conv_kernel<CONV_ADD_INPUT><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
-        default: causal_conv_kernel<CONV_SILU | CONV_ADD_INPUT><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs); break;
+        case 0: causal_conv_kernel<0><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs, own); break;
+        case CONV_SILU: causal_conv_kernel<CONV_SILU><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs, own); break;
+        case CONV_ADD_INPUT: causal_conv_kernel<CONV_ADD_INPUT><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs, own); break;
+        default: causal_conv_kernel<CONV_SILU | CONV_ADD_INPUT><<<grid, 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs, own); break;
     }
     B2_LAUNCH_CHECK();
-    if (taps > 1) {
+    if (taps > 1 && !own) {
         causal_conv_tail_kernel<<<dim3((C + 127) / 128, nseg), 128, 0, st>>>(in, ld_in, tail, C, taps, segs);
         B2_LAUNCH_CHECK();
     }

@@ -17,7 +17,11 @@ namespace {
 
 // Units of a head: single elements outside the rotated range, pairs inside it, so that a thread owns everything it reads and
 // the call may run in place.
-__global__ void __launch_bounds__(256) rotate_rows_kernel(RotateArgs a) {
+struct RotateParts { RotateArgs p[3]; };
+__device__ __forceinline__ void rotate_rows_body(const RotateArgs& a);
+__global__ void __launch_bounds__(256) rotate_rows_kernel(RotateArgs a) { rotate_rows_body(a); }
+__global__ void __launch_bounds__(256) rotate_rows_multi_kernel(RotateParts ps) { rotate_rows_body(ps.p[blockIdx.z]); }
+__device__ __forceinline__ void rotate_rows_body(const RotateArgs& a) {
     const int units = a.size - a.pairs;
     const int r = blockIdx.y;
     const int pos = a.row_pos[r];
@@ -84,6 +88,23 @@ int rotate_rows_f32(const RotateArgs& a, cudaStream_t st) {
     B2_CHECK_ARG(a.cache == nullptr || (a.row_slot != nullptr && a.Smax > 0), "rotate_rows: a cache destination needs slots");
     const int units = a.heads * (a.size - a.pairs);
     rotate_rows_kernel<<<dim3((units + 255) / 256, a.rows), 256, 0, st>>>(a);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int rotate_rows_multi_f32(const RotateArgs* parts, int n, cudaStream_t st) {
+    B2_CHECK_ARG(parts && n >= 1 && n <= 3, "rotate_rows_multi: 1..3 parts");
+    RotateParts ps;
+    int units = 0;
+    for (int i = 0; i < n; ++i) {
+        const RotateArgs& a = parts[i];
+        B2_CHECK_ARG(a.in && (a.out || a.cache) && (a.table || a.pairs == 0) && a.row_pos && a.rows == parts[0].rows && a.heads > 0 && a.size > 0, "rotate_rows_multi: bad argument");
+        B2_CHECK_ARG(a.pairs >= 0 && a.offset >= 0 && a.offset + 2 * a.pairs <= a.size, "rotate_rows_multi: %d pairs from %d do not fit a head of %d", a.pairs, a.offset, a.size);
+        B2_CHECK_ARG(a.cache == nullptr || (a.row_slot != nullptr && a.Smax > 0), "rotate_rows_multi: a cache destination needs slots");
+        ps.p[i] = a;
+        units = std::max(units, a.heads * (a.size - a.pairs));
+    }
+    rotate_rows_multi_kernel<<<dim3((units + 255) / 256, parts[0].rows, n), 256, 0, st>>>(ps);
     B2_LAUNCH_CHECK();
     return 0;
 }

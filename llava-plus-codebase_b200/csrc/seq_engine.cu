@@ -341,18 +341,16 @@ static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& 
         ldc = L.conv_ch;
         B2_TRY(causal_conv_f32(proj, L.lproj_ld, W.conv_w.as<float>(), nullptr, S.conv_tail.as<float>(), qkv, ldc, L.conv_ch, d.ga_conv, 0, segs, nseg, max_n, st));
     }
-    RotateArgs ra;
-    ra.table = S.rot_tab.as<float2>(); ra.pairs = d.rot_dims / 2; ra.offset = 0; ra.rows = R; ra.row_slot = row_slot; ra.row_pos = row_pos; ra.Smax = kv->max_seq;
-    ra.size = dk;
-    // queries in place, keys into the cache
-    ra.in = qkv; ra.ld_in = ldc; ra.hs_in = dk; ra.out = qkv; ra.ld_out = ldc; ra.hs_out = dk; ra.heads = H;
-    if (ra.pairs > 0) B2_TRY(rotate_rows_f32(ra, st));
-    ra.in = qkv + L.nq; ra.out = nullptr; ra.cache = S.kc.as<float>(); ra.heads = G;
-    B2_TRY(rotate_rows_f32(ra, st));
-    // values into the cache, turned by their own position over all of vdim when the design says so
-    ra.in = qkv + L.nq + L.nk; ra.hs_in = dv; ra.cache = S.vc.as<float>(); ra.size = dv;
-    ra.table = S.vrot_tab.as<float2>(); ra.pairs = d.ga_rot_values ? dv / 2 : 0;
-    B2_TRY(rotate_rows_f32(ra, st));
+    // queries in place, keys into the cache, values into the cache (turned by their own position over all of vdim when the design
+    // says so): one launch
+    RotateArgs rq[3];
+    for (RotateArgs& ra : rq) { ra.rows = R; ra.row_slot = row_slot; ra.row_pos = row_pos; ra.Smax = kv->max_seq; ra.ld_in = ldc; ra.offset = 0; }
+    rq[0].in = qkv; rq[0].hs_in = dk; rq[0].out = qkv; rq[0].ld_out = ldc; rq[0].hs_out = dk; rq[0].heads = H; rq[0].size = dk;
+    rq[1].in = qkv + L.nq; rq[1].hs_in = dk; rq[1].cache = S.kc.as<float>(); rq[1].heads = G; rq[1].size = dk;
+    rq[0].table = rq[1].table = S.rot_tab.as<float2>(); rq[0].pairs = rq[1].pairs = d.rot_dims / 2;
+    rq[2].in = qkv + L.nq + L.nk; rq[2].hs_in = dv; rq[2].cache = S.vc.as<float>(); rq[2].heads = G; rq[2].size = dv;
+    rq[2].table = S.vrot_tab.as<float2>(); rq[2].pairs = d.ga_rot_values ? dv / 2 : 0;
+    B2_TRY(rotate_rows_multi_f32(rq, 3, st));
     BiasAttnArgs aa;
     aa.q = qkv; aa.ldq = ldc;
     aa.kcache = S.kc.as<float>(); aa.vcache = S.vc.as<float>();
@@ -375,6 +373,29 @@ static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& 
     rb.rows = R; rb.row_pos = row_pos;
     B2_TRY(rotate_rows_f32(rb, st));
     return lin(s.gated.as<float>(), L.ng, W.o_w, width, L.ng, target, width, R, LIN_NONE, alpha, accumulate);
+}
+
+// What a sublayer of a sandwich block reads: the pending sublayer output (weight `post`, in mixout) joins x, x is normed with
+// `norm` into xn, and the input convolution adds to it (a decode step: in the same launch). *h: where the result lies.
+static int sandwich_input(SeqModel& s, const float* post, const DevBuf& norm, const DevBuf& taps_w, DevBuf& tail, int R, int nseg, int max_n,
+                          cudaStream_t st, const float** h) {
+    const int width = s.d.width, ctaps = s.d.input_conv_taps;
+    SandwichNormArgs na;
+    if (post != nullptr) { na.y = s.mixout.as<float>(); na.w_post = post; }
+    na.x = s.x.as<float>(); na.w_pre = norm.as<float>(); na.out = s.xn.as<float>(); na.rows = R; na.cols = width; na.eps = s.d.norm_eps;
+    *h = s.xn.as<float>();
+    if (ctaps > 1 && max_n == 1) {
+        na.conv_w = taps_w.as<float>(); na.tail = tail.as<float>(); na.taps = ctaps; na.segs = s.segs.as<SeqSeg>(); na.conv_out = s.hin.as<float>();
+        *h = s.hin.as<float>();
+        return sandwich_norm_f32(na, st);
+    }
+    B2_TRY(sandwich_norm_f32(na, st));
+    if (ctaps > 1) {
+        B2_TRY(causal_conv_f32(s.xn.as<float>(), width, taps_w.as<float>(), nullptr, tail.as<float>(), s.hin.as<float>(), width, width, ctaps, CONV_ADD_INPUT,
+                               s.segs.as<SeqSeg>(), nseg, max_n, st));
+        *h = s.hin.as<float>();
+    }
+    return 0;
 }
 
 // The feed-forward of a pre-norm or sandwich block in its three kinds.
@@ -497,6 +518,7 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
     const bool pre = s.d.block == B2_BLOCK_PRE_RMS1, sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS;
     const float rm = s.d.residual_mult;
     float* xn = s.xn.as<float>();
+    const float* post = nullptr;   // sandwich block: weight of the sublayer output in `mix` that has not joined x yet
     for (size_t ri = 0; ri < s.runs.size(); ++ri) {
         const size_t li = (size_t)s.runs[ri].layer;
         const SeqLayerInfo& L = s.layers[li];
@@ -509,21 +531,13 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
         const float* pass_vec = pass >= 0 ? s.loop_step.as<float>() + (size_t)pass * width : nullptr;
         if (pre || sandwich) {
             // pre-norm block: a sublayer reads g * unit_rms(x) and adds residual_mult * its output onto x in its last product.
-            // sandwich block: a sublayer reads u + conv(u), u = rms_w(x); its output lands in `mix` and its weighted RMS norm joins x.
-            const int ctaps = s.d.input_conv_taps;
+            // sandwich block: a sublayer reads u + conv(u), u = rms_w(x); its output lands in `mix`, and its weighted RMS norm joins x in
+            // the same pass that norms x for the next sublayer (`post`: the weight of a sublayer output that has not joined x yet).
             float* target = pre ? x : mix;
             const float alpha = pre ? rm : 1.f;
             const float* h = xn;
-            if (pre) {
-                B2_TRY(rms_scalar_f32(x, nullptr, W.norm1.as<float>(), pass_add, pass_vec, xn, R, width, eps, st));
-            } else {
-                B2_TRY(rms_weight_f32(x, width, nullptr, W.norm1.as<float>(), xn, width, 0, R, width, eps, st));
-                if (ctaps > 1) {
-                    B2_TRY(causal_conv_f32(xn, width, W.canon1.as<float>(), nullptr, S.canon1.as<float>(), s.hin.as<float>(), width, width, ctaps, CONV_ADD_INPUT,
-                                           segs, nseg, max_n, st));
-                    h = s.hin.as<float>();
-                }
-            }
+            if (pre) B2_TRY(rms_scalar_f32(x, nullptr, W.norm1.as<float>(), pass_add, pass_vec, xn, R, width, eps, st));
+            else B2_TRY(sandwich_input(s, post, W.norm1, W.canon1, S.canon1, R, nseg, max_n, st, &h));
             if (d.type == B2_MIXER_LATENT_ATTN) {
                 SeqLayerState& KS = d.la_kv_from > 0 ? state.layer[s.runs[ri].kv_run] : S;
                 B2_TRY(latent_mixer(m, kv, L, W, S, KS, h, target, alpha, pre ? 1 : 0, R, nseg, slot, ctx_end, st));
@@ -547,21 +561,19 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                 B2_TRY(group_rmsnorm_f32(s.y.as<float>(), L.pv, W.hnorm.as<float>(), 1, s.gated.as<float>(), L.pv, R, L.pv, dv, eps, st));
                 B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, target, width, R, LIN_NONE, alpha, pre ? 1 : 0));
             }
-            if (sandwich) B2_TRY(rms_weight_f32(mix, width, nullptr, W.norm1_b.as<float>(), x, width, 1, R, width, eps, st));
+            post = sandwich ? W.norm1_b.as<float>() : nullptr;
             if (d.ff > 0) {
                 h = xn;
-                if (pre) {
-                    B2_TRY(rms_scalar_f32(x, nullptr, W.norm2.as<float>(), nullptr, nullptr, xn, R, width, eps, st));
-                } else {
-                    B2_TRY(rms_weight_f32(x, width, nullptr, W.norm2.as<float>(), xn, width, 0, R, width, eps, st));
-                    if (ctaps > 1) {
-                        B2_TRY(causal_conv_f32(xn, width, W.canon2.as<float>(), nullptr, S.canon2.as<float>(), s.hin.as<float>(), width, width, ctaps,
-                                               CONV_ADD_INPUT, segs, nseg, max_n, st));
-                        h = s.hin.as<float>();
-                    }
-                }
+                if (pre) B2_TRY(rms_scalar_f32(x, nullptr, W.norm2.as<float>(), nullptr, nullptr, xn, R, width, eps, st));
+                else B2_TRY(sandwich_input(s, post, W.norm2, W.canon2, S.canon2, R, nseg, max_n, st, &h));
                 B2_TRY(seq_feed_forward(m, L, W, h, target, alpha, pre ? 1 : 0, R, st));
-                if (sandwich) B2_TRY(rms_weight_f32(mix, width, nullptr, W.norm2_b.as<float>(), x, width, 1, R, width, eps, st));
+                post = sandwich ? W.norm2_b.as<float>() : nullptr;
+            }
+            if (post != nullptr && (resid_out != nullptr || ri + 1 == s.runs.size())) {   // the last sublayer's output joins x now
+                SandwichNormArgs na;
+                na.y = mix; na.w_post = post; na.x = x; na.rows = R; na.cols = width; na.eps = eps;
+                B2_TRY(sandwich_norm_f32(na, st));
+                post = nullptr;
             }
             if (resid_out != nullptr)
                 B2_CUDA_CHECK(cudaMemcpyAsync(resid_out + ri * (size_t)R * width, x, (size_t)R * width * F4, cudaMemcpyDeviceToDevice, st));
