@@ -214,7 +214,7 @@ int b2_batch_set_row(b2_model* m, b2_kv* kv, int slot, int active, const b2_samp
  * Blocks: B2_BLOCK_POST_LN adds the LayerNorm of every sublayer's OUTPUT; B2_BLOCK_PRE_RMS1 is pre-norm,
  * x += residual_mult * sublayer(g * unit_rms(x)) with ONE learned number g per norm (also in front of the head);
  * B2_BLOCK_SANDWICH_RMS norms both sides with weighted RMS norms, x += rms_w'(sublayer(u + conv(u))), u = rms_w(x), where
- * conv is a causal depthwise convolution over time of input_conv_taps taps (0: none) whose last taps - 1 inputs are carried
+ * conv is a causal depthwise convolution over time of input_conv_taps taps (0: none; 1: a factor per channel) whose last taps - 1 inputs are carried
  * per slot, for the mixer and for the feed-forward of every layer.
  * Feed-forwards: B2_FF_RELU_SQ (W_down relu(W_up x)^2), B2_FF_POLYNORM (biased projections around
  * a N(z) + b N(z^2) + c N(z^3) + e, N = division by the token's root mean square), B2_FF_MOE (router, group-limited
@@ -266,7 +266,7 @@ typedef struct b2_seq_layer_desc {
     int32_t la_q_rank, la_rot_dim, la_no_sink, la_no_gate;
     int32_t la_kv_from;      /* 1 + the earlier layer whose cache rows this layer reads; 0: its own */
     /* B2_MIXER_GQA_ATTN */
-    int32_t ga_heads, ga_kv_heads, ga_dim, ga_vdim, ga_conv;   /* ga_conv: taps of the convolution on q, k, v (<= 1: none) */
+    int32_t ga_heads, ga_kv_heads, ga_dim, ga_vdim, ga_conv;   /* ga_conv: taps of the convolution on q, k, v (0: none) */
     int32_t ga_rot_values, ga_sink;
     float ga_scale, ga_sink_value;
     /* visible keys and rotation of the attention mixers above */
@@ -287,7 +287,7 @@ typedef struct b2_seq_model_desc {
                                                                  buckets, row `buckets` for a sequence's first token; 0 buckets = none */
     int32_t loop_start, loop_stop, loop_times;                /* layers [start, stop) run `times` times in a row; times 0: no loop */
     float logit_scale;       /* factor on the logits; 0 = 1 */
-    int32_t input_conv_taps; /* B2_BLOCK_SANDWICH_RMS: taps of the convolution every sublayer's input passes (<= 1: none) */
+    int32_t input_conv_taps; /* B2_BLOCK_SANDWICH_RMS: taps of the convolution every sublayer's input passes (0: none) */
 } b2_seq_model_desc;
 int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* layers, b2_model** out);
 /* Layer RUNS of one forward pass (a looped layer counts every time): rows of b2_append_tokens' resid_out; -1 for other models */

@@ -189,7 +189,7 @@ __global__ void sandwich_norm_kernel(SandwichNormArgs a) {
             acc = fmaf(wc[j], old, acc);
             if (j > 0) tl[(size_t)(j - 1) * cols + c] = old;
         }
-        tl[(size_t)(taps - 2) * cols + c] = v;
+        if (taps > 1) tl[(size_t)(taps - 2) * cols + c] = v;
         co[c] = acc;
     }
 }
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(512) sandwich_norm_reg_kernel(SandwichNormArgs
             const int tj = j - (TP - (taps - 1));
             if (tj >= 1) tl[(size_t)(tj - 1) * cols + c] = old[j][i];
         }
-        tl[(size_t)(taps - 2) * cols + c] = xv[i];
+        if (taps > 1) tl[(size_t)(taps - 2) * cols + c] = xv[i];
         co[c] = acc;
     }
 }
@@ -485,7 +485,7 @@ int rms_weight_f32(const float* in, int64_t ld_in, const int32_t* row_index, con
 
 int sandwich_norm_f32(const SandwichNormArgs& a, cudaStream_t st) {
     B2_CHECK_ARG(a.x && a.rows > 0 && a.cols > 0 && (a.y == nullptr) == (a.w_post == nullptr) && (a.w_pre == nullptr || a.out != nullptr), "sandwich_norm: bad argument");
-    B2_CHECK_ARG(a.conv_w == nullptr || (a.w_pre && a.tail && a.segs && a.conv_out && a.taps >= 2 && a.taps <= 16), "sandwich_norm: the fused convolution needs taps, tail and segments");
+    B2_CHECK_ARG(a.conv_w == nullptr || (a.w_pre && (a.tail || a.taps == 1) && a.segs && a.conv_out && a.taps >= 1 && a.taps <= 16), "sandwich_norm: the fused convolution needs taps, tail and segments");
     // rows of up to 4096 entries live in registers (4 entries per thread for narrow rows, 8 otherwise); the fused convolution rides in
     // that kernel with up to 4 taps, and in the plain one otherwise
     const bool conv = a.conv_w != nullptr;

@@ -336,7 +336,7 @@ static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& 
     B2_TRY(lin(h, width, W.lproj_w, L.lproj, width, proj, L.lproj_ld, R));
     float* qkv = proj;
     int64_t ldc = L.lproj_ld;
-    if (d.ga_conv > 1) {
+    if (d.ga_conv >= 1) {
         qkv = s.act.as<float>();
         ldc = L.conv_ch;
         B2_TRY(causal_conv_f32(proj, L.lproj_ld, W.conv_w.as<float>(), nullptr, S.conv_tail.as<float>(), qkv, ldc, L.conv_ch, d.ga_conv, 0, segs, nseg, max_n, st));
@@ -384,13 +384,13 @@ static int sandwich_input(SeqModel& s, const float* post, const DevBuf& norm, co
     if (post != nullptr) { na.y = s.mixout.as<float>(); na.w_post = post; }
     na.x = s.x.as<float>(); na.w_pre = norm.as<float>(); na.out = s.xn.as<float>(); na.rows = R; na.cols = width; na.eps = s.d.norm_eps;
     *h = s.xn.as<float>();
-    if (ctaps > 1 && max_n == 1) {
+    if (ctaps >= 1 && max_n == 1) {
         na.conv_w = taps_w.as<float>(); na.tail = tail.as<float>(); na.taps = ctaps; na.segs = s.segs.as<SeqSeg>(); na.conv_out = s.hin.as<float>();
         *h = s.hin.as<float>();
         return sandwich_norm_f32(na, st);
     }
     B2_TRY(sandwich_norm_f32(na, st));
-    if (ctaps > 1) {
+    if (ctaps >= 1) {
         B2_TRY(causal_conv_f32(s.xn.as<float>(), width, taps_w.as<float>(), nullptr, tail.as<float>(), s.hin.as<float>(), width, width, ctaps, CONV_ADD_INPUT,
                                s.segs.as<SeqSeg>(), nseg, max_n, st));
         *h = s.hin.as<float>();
@@ -758,11 +758,11 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
             const int ct = s.d.input_conv_taps;
             if (r == "norm1") return vec(W.norm1, width);
             if (r == "norm1b") return vec(W.norm1_b, width);
-            if (r == "canon1" && ct > 1) return taps_of(W.canon1, width, width, 0, ct);
+            if (r == "canon1" && ct >= 1) return taps_of(W.canon1, width, width, 0, ct);
             if (d.ff > 0) {
                 if (r == "norm2") return vec(W.norm2, width);
                 if (r == "norm2b") return vec(W.norm2_b, width);
-                if (r == "canon2" && ct > 1) return taps_of(W.canon2, width, width, 0, ct);
+                if (r == "canon2" && ct >= 1) return taps_of(W.canon2, width, width, 0, ct);
             }
         } else {
             if (r == "norm1") return vec(W.norm1, 1);
@@ -816,7 +816,7 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
             int row0 = 0;
             for (int j = 0; j < 4; ++j) {
                 if (r == parts[j]) return part(W.lproj_w, L.lproj, row0, sizes[j], width);
-                if (j < 3 && d.ga_conv > 1 && r == std::string(parts[j]) + ".conv") return taps_of(W.conv_w, sizes[j], L.conv_ch, row0, d.ga_conv);
+                if (j < 3 && d.ga_conv >= 1 && r == std::string(parts[j]) + ".conv") return taps_of(W.conv_w, sizes[j], L.conv_ch, row0, d.ga_conv);
                 row0 += sizes[j];
             }
             if (r == "mix.o") return mat(W.o_w, width, L.ng);
@@ -934,7 +934,7 @@ static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre, boo
     if (pre) {
         std::vector<std::string> v = {"norm1", "mix.o"};
         const b2_seq_layer_desc& d = L.d;
-        if (sandwich) { v.push_back("norm1b"); if (ctaps > 1) v.push_back("canon1"); }
+        if (sandwich) { v.push_back("norm1b"); if (ctaps >= 1) v.push_back("canon1"); }
         if (d.type == B2_MIXER_LATENT_ATTN) {
             for (const char* n : {"mix.uk", "mix.uv"}) v.push_back(n);
             if (d.la_q_rank > 0) for (const char* n : {"mix.dq", "mix.dq.norm", "mix.uq"}) v.push_back(n);
@@ -944,11 +944,11 @@ static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre, boo
             if (!d.la_no_gate) v.push_back("mix.g");
         } else if (d.type == B2_MIXER_GQA_ATTN) {
             for (const char* n : {"mix.q", "mix.k", "mix.v", "mix.g"}) v.push_back(n);
-            if (d.ga_conv > 1) for (const char* n : {"mix.q.conv", "mix.k.conv", "mix.v.conv"}) v.push_back(n);
+            if (d.ga_conv >= 1) for (const char* n : {"mix.q.conv", "mix.k.conv", "mix.v.conv"}) v.push_back(n);
         } else for (const char* n : {"mix.q", "mix.f", "mix.f.b", "mix.lower", "mix.v", "mix.norm"}) v.push_back(n);
         if (L.d.ff > 0) {
             v.push_back("norm2");
-            if (sandwich) { v.push_back("norm2b"); if (ctaps > 1) v.push_back("canon2"); }
+            if (sandwich) { v.push_back("norm2b"); if (ctaps >= 1) v.push_back("canon2"); }
             if (L.d.ff_kind == B2_FF_POLYNORM) for (const char* n : {"mlp.up", "mlp.up.b", "mlp.down", "mlp.down.b", "mlp.act"}) v.push_back(n);
             else if (L.d.ff_kind == B2_FF_MOE) {
                 v.push_back("mlp.router");
@@ -1035,7 +1035,7 @@ int seq_finalize(b2_model* m) {
     B2_TRY(s.ff.alloc(R * fw * F4));
     B2_TRY(s.xn.alloc(R * width * F4));
     if (pre) B2_TRY(s.ffa.alloc(R * fw * F4));
-    if (sandwich && s.d.input_conv_taps > 1) B2_TRY(s.hin.alloc(R * width * F4));
+    if (sandwich && s.d.input_conv_taps >= 1) B2_TRY(s.hin.alloc(R * width * F4));
     if (s.d.loop_times > 1) B2_TRY(s.x0.alloc(R * width * F4));
     if (latw > 0) {
         s.lat_w = latw;
@@ -1247,7 +1247,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
     B2_CHECK_ARG(d.norm_eps >= 0.f, "b2_seq_model_create: negative eps");
     B2_CHECK_ARG(d.block == B2_BLOCK_POST_LN || d.block == B2_BLOCK_PRE_RMS1 || d.block == B2_BLOCK_SANDWICH_RMS, "b2_seq_model_create: unknown block form %d", d.block);
     B2_CHECK_ARG(d.input_conv_taps >= 0 && d.input_conv_taps <= 16, "b2_seq_model_create: 0..16 taps of the input convolution");
-    B2_CHECK_ARG(d.input_conv_taps <= 1 || d.block == B2_BLOCK_SANDWICH_RMS, "b2_seq_model_create: the input convolution belongs to the sandwich block");
+    B2_CHECK_ARG(d.input_conv_taps == 0 || d.block == B2_BLOCK_SANDWICH_RMS, "b2_seq_model_create: the input convolution belongs to the sandwich block");
     B2_CHECK_ARG(d.bigram_buckets >= 0 && d.logit_softcap >= 0.f, "b2_seq_model_create: negative bigram buckets or soft-cap");
     SeqModel* s = new SeqModel();
     s->d = d;

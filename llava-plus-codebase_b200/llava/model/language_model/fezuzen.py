@@ -44,14 +44,20 @@ class FezuzenConfig(LayerListConfig):
         return dict(block=BLOCK_SANDWICH_RMS, logit_scale=float(c.get("logit_scale", 1.0)),
                     input_conv_taps=int((c.get("canon") or {}).get("taps", 0)))
 
+    @staticmethod
+    def _conv_taps(i, mix, shapes):
+        """Taps of the short convolution on q / k / v: `mixer.conv`, or what the checkpoint's tensor says when the key is absent."""
+        if mix.get("conv") is not None:
+            return int(mix["conv"])
+        shape = shapes.get(f"l{i}.mix.q.conv")
+        return int(shape[1]) if shape else 0
+
     def layer_descs(self, shapes):
         out = []
         for i, layer in enumerate(self.layers):
             mix, mlp = layer["mixer"], layer.get("mlp")
             d = dict(weights_of=-1, ff=0)
             if layer["type"] == "latent_attention":
-                if int(mix["rot"]["dims"]) != int(mix["rot_dim"]):
-                    raise ValueError(f"layer {i}: the rotated key part has rot_dim = {mix['rot_dim']} entries but rot.dims = {mix['rot']['dims']}")
                 src = mix.get("kv_from")
                 d.update(type=MIXER_LATENT_ATTN, la_heads=int(mix["heads"]), la_dim=int(mix["dim"]), la_vdim=int(mix["vdim"]),
                          la_rank=int(mix["kv_rank"]), la_scale=float(mix["scale"]), la_q_rank=int(mix["q_rank"]),
@@ -59,7 +65,7 @@ class FezuzenConfig(LayerListConfig):
                          **_rotation(mix["rot"], f"layer {i}"), **_mask(mix, MASK_WINDOW))
             elif layer["type"] == "attention":
                 d.update(type=MIXER_GQA_ATTN, ga_heads=int(mix["heads"]), ga_kv_heads=int(mix["kv_heads"]), ga_dim=int(mix["dim"]),
-                         ga_vdim=int(mix["vdim"]), ga_conv=int(mix.get("conv", 0) or 0), ga_rot_values=1, ga_sink=1, ga_sink_value=0.0,
+                         ga_vdim=int(mix["vdim"]), ga_conv=self._conv_taps(i, mix, shapes), ga_rot_values=1, ga_sink=1, ga_sink_value=0.0,
                          ga_scale=float(mix["scale"]), **_rotation(mix["rot"], f"layer {i}"), **_mask(mix, MASK_CHUNK))
             else:
                 raise NotImplementedError(f"layer {i}: mixer type {layer['type']!r}")

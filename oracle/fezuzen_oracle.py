@@ -141,7 +141,7 @@ def grouped_attention(h, p, mix, extra_one=True):
     scale, size = float(mix["scale"]), mask_size(mix)
     freq, mag = rotary_frequencies(mix["rot"])
     vfreq = np.array([float(mix["rot"]["base"]) ** (-2.0 * m / dv) for m in range(dv // 2)], F)
-    conv = (lambda u, n: causal_conv(u, p[n + ".conv"])) if int(mix.get("conv", 0) or 0) > 1 else (lambda u, n: u)
+    conv = (lambda u, n: causal_conv(u, p[n + ".conv"])) if int(mix.get("conv", 0) or 0) >= 1 else (lambda u, n: u)
     q = conv(h @ p["q"].T, "q").reshape(T, H, dk)
     k = conv(h @ p["k"].T, "k").reshape(T, G, dk)
     v = conv(h @ p["v"].T, "v").reshape(T, G, dv)
@@ -252,7 +252,7 @@ def tensor_shapes(cfg):
         mix, mlp = layer["mixer"], layer.get("mlp")
         a = f"l{i}."
         out[a + "norm1"] = out[a + "norm1b"] = (width,)
-        if ct > 1:
+        if ct >= 1:
             out[a + "canon1"] = (width, ct)
         if layer["type"] == "latent_attention":
             H, dk, rd, dv, rank, qr = (int(mix[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"))
@@ -265,12 +265,12 @@ def tensor_shapes(cfg):
             taps = int(mix.get("conv", 0) or 0)
             for n, rows in (("q", H * dk), ("k", G * dk), ("v", G * dv)):
                 out[a + "mix." + n] = (rows, width)
-                if taps > 1:
+                if taps >= 1:
                     out[a + "mix." + n + ".conv"] = (rows, taps)
             out[a + "mix.g"], out[a + "mix.o"] = (H * dv, width), (width, H * dv)
         if mlp:
             out[a + "norm2"] = out[a + "norm2b"] = (width,)
-            if ct > 1:
+            if ct >= 1:
                 out[a + "canon2"] = (width, ct)
             ff = int(mlp["expert"]["ff"])
             out[a + "mlp.router"] = (int(mlp["router"]["experts"]), width)

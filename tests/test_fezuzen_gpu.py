@@ -44,6 +44,7 @@ LAT_MANY = latent(40, 8, 4, 4, 24, 24, 50, scaling=YARN)                   # mor
 LAT_WIDE = latent(2, 32, 16, 48, 288, 64, 19)                              # cached rows wider than 256
 GQA = grouped(6, 2, 16, 24, 3, 11, 8, scaling=YARN)                        # part of a head rotated, keys with scaled frequencies
 GQA_ODD = grouped(2, 2, 7, 6, 0, 5, 4)                                     # groups of one head, no convolution, odd head size
+GQA_TAP = grouped(3, 1, 8, 4, 1, 1, 2)                                     # a convolution of ONE tap, chunks of one position, one rotated pair
 GQA_ONE_KV = grouped(4, 1, 12, 10, 2, 64, 12, base=1.0e6)                  # one key/value head, all of a head rotated
 GQA_BIG = grouped(3, 3, 40, 136, 5, 29, 40)                                # values wider than 128
 MOE = {"kind": "moe", "expert": {"ff": 24}, "shared": {"ff": 40}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
@@ -68,7 +69,7 @@ def config(layers, width=72, vocab=150, eps=1e-5, taps=3, logit_scale=0.7):
 CFG_MAIN = config([layer(LAT, MOE), layer(GQA, MOE_ALL), layer(latent(2, 24, 8, 8, 40, 16, 30, scaling=YARN, kv_from=0), None), layer(GQA_ONE_KV, MOE)], width=64)
 CFG_ODD = config([layer(GQA_ODD, MOE_ONE), layer(LAT_ODD, MOE_SINGLES), layer(latent(3, 5, 6, 9, 21, 7, 4, base=10000.0, kv_from=1), MOE_ONE)],
                  width=50, vocab=77, eps=1e-3, taps=2, logit_scale=None)
-CFG_NO_CONV = config([layer(LAT_ONE, None), layer(GQA_BIG, MOE_SINGLES), layer(LAT_MANY, None)], width=48, taps=1, logit_scale=2.5)
+CFG_ONE_TAP = config([layer(LAT_ONE, None), layer(GQA_BIG, MOE_SINGLES), layer(LAT_MANY, None), layer(GQA_TAP, MOE_ONE)], width=48, taps=1, logit_scale=2.5)
 CFG_TAPS = config([layer(GQA_ONE_KV, None), layer(LAT_WIDE, MOE)], width=56, taps=6)
 
 
@@ -123,13 +124,13 @@ def run_schedule(eng, kv, slot, toks, cuts, decode_single=True):
 
 # ----------------------------------------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["latent", "latent_odd", "latent_one", "latent_many", "latent_wide", "gqa", "gqa_odd", "gqa_one_kv", "gqa_big",
+@pytest.mark.parametrize("name", ["latent", "latent_odd", "latent_one", "latent_many", "latent_wide", "gqa", "gqa_odd", "gqa_one_kv", "gqa_big", "gqa_tap",
                                   "moe", "moe_top1", "moe_singles", "moe_all"])
 def test_each_mechanism_alone(name, dtype):
     """One layer: the residual stream after it equals the oracle's x + norm_b(mechanism(u + conv(u))), u = norm(x), built here from
     the oracle's function for that mechanism."""
     mixers = {"latent": LAT, "latent_odd": LAT_ODD, "latent_one": LAT_ONE, "latent_many": LAT_MANY, "latent_wide": LAT_WIDE, "gqa": GQA,
-              "gqa_odd": GQA_ODD, "gqa_one_kv": GQA_ONE_KV, "gqa_big": GQA_BIG}
+              "gqa_odd": GQA_ODD, "gqa_one_kv": GQA_ONE_KV, "gqa_big": GQA_BIG, "gqa_tap": GQA_TAP}
     mlps = {"moe": MOE, "moe_top1": MOE_ONE, "moe_singles": MOE_SINGLES, "moe_all": MOE_ALL}
     lay = layer(mixers.get(name, GQA_ODD), mlps.get(name))
     cfg = config([lay], width=50 if name.endswith("odd") else 72, taps=4 if "gqa" in name else 3)
@@ -161,8 +162,8 @@ def test_router_choices_and_weights():
 
 
 # ----------------------------------------------------------------------------------------------------------- whole models
-ALL_CFGS = [CFG_MAIN, CFG_ODD, CFG_NO_CONV, CFG_TAPS]
-ALL_IDS = ["main", "odd", "no_conv", "taps"]
+ALL_CFGS = [CFG_MAIN, CFG_ODD, CFG_ONE_TAP, CFG_TAPS]
+ALL_IDS = ["main", "odd", "one_tap", "taps"]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
