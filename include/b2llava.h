@@ -271,7 +271,7 @@ typedef struct b2_seq_layer_desc {
     float ga_scale, ga_sink_value;
     /* visible keys and rotation of the attention mixers above */
     int32_t mask_kind, mask_size;   /* B2_MASK_* */
-    int32_t rot_dims;               /* rotated leading dimensions of a head (of the rotated part, for latent attention); even */
+    int32_t rot_dims;               /* rotated leading dimensions of a head (of the rotated part, for latent attention); an odd last one passes */
     float rot_base, rot_factor, rot_original, rot_fast, rot_slow;   /* rot_factor 0: plain frequencies */
 } b2_seq_layer_desc;
 typedef struct b2_seq_model_desc {

@@ -402,7 +402,7 @@ struct SandwichNormArgs {
 int sandwich_norm_f32(const SandwichNormArgs& a, cudaStream_t stream);
 
 // ---- rotary positions (rotary.cu) -------------------------------------------------------------------------------------------
-// Pairs (2m, 2m+1), m < dims / 2, turn by position * f_m, f_m = base^(-2m / dims). factor > 0: f_m is blended towards f_m / factor
+// Pairs (2m, 2m+1), m < floor(dims / 2), turn by position * f_m, f_m = base^(-2m / dims). factor > 0: f_m is blended towards f_m / factor
 // over the pairs between lo = max(floor(dim(fast)), 0) and hi = min(ceil(dim(slow)), dims - 1), dim(t) = dims ln(original / (2 pi t)) /
 // (2 ln base), and cos / sin are scaled by 0.1 ln(factor) + 1.
 struct RotaryDesc { int dims = 0; float base = 10000.f, factor = 0.f, original = 0.f, fast = 0.f, slow = 0.f; };
@@ -424,10 +424,10 @@ struct RotateArgs {
 int rotate_rows_f32(const RotateArgs& a, cudaStream_t stream);
 // up to three such calls over the same rows in one launch (queries, keys and values of an attention layer)
 int rotate_rows_multi_f32(const RotateArgs* parts, int n, cudaStream_t stream);
-// Row of a low-rank key/value cache with a rotated key part: cache[slot][pos] = [unit_rms(in[r, :rank]) * gamma | the 2 * pairs entries
-// behind them turned by the row's position]; rows of the cache have rank + 2 * pairs entries
+// Row of a low-rank key/value cache with a rotated key part: cache[slot][pos] = [unit_rms(in[r, :rank]) * gamma | the rot entries
+// behind them, of which the first `pairs` pairs are turned by the row's position]; rows of the cache have rank + rot entries
 int latent_rot_append_f32(const float* in, int64_t ld_in, const float* gamma, float* cache, const int32_t* row_slot, const int32_t* row_pos, int rows,
-                          int rank, int pairs, const float2* table, int Smax, float eps, cudaStream_t stream);
+                          int rank, int rot, int pairs, const float2* table, int Smax, float eps, cudaStream_t stream);
 
 // ---- recurrent mixers (recurrent.cu) ----------------------------------------------------------------------------------
 // Causal depthwise convolution + SiLU with a carried tail: out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]);

@@ -55,10 +55,10 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// cache[slot][pos] = [ unit_rms(in[r, :rank]) * gamma | rotate(in[r, rank : rank + 2 * pairs], pos) ]
+// cache[slot][pos] = [ unit_rms(in[r, :rank]) * gamma | the rot entries behind them, their first `pairs` pairs turned by pos ]
 __global__ void __launch_bounds__(128) latent_rot_append_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ gamma,
                                                                 float* __restrict__ cache, const int32_t* __restrict__ row_slot,
-                                                                const int32_t* __restrict__ row_pos, int rank, int pairs,
+                                                                const int32_t* __restrict__ row_pos, int rank, int rot, int pairs,
                                                                 const float2* __restrict__ table, int Smax, float eps) {
     __shared__ float red[4];
     const size_t r = blockIdx.x;
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(128) latent_rot_append_kernel(const float* __r
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
     __syncthreads();
     const float mul = 1.f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)rank + eps);
-    float* dst = cache + ((size_t)row_slot[r] * Smax + pos) * (rank + 2 * pairs);
+    float* dst = cache + ((size_t)row_slot[r] * Smax + pos) * (rank + rot);
     for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = src[c] * mul * gamma[c];
     for (int mp = threadIdx.x; mp < pairs; mp += blockDim.x) {
         const float2 cs = table[(size_t)pos * pairs + mp];
@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(128) latent_rot_append_kernel(const float* __r
         dst[rank + 2 * mp] = x * cs.x - y * cs.y;
         dst[rank + 2 * mp + 1] = y * cs.x + x * cs.y;
     }
+    for (int c = rank + 2 * pairs + threadIdx.x; c < rank + rot; c += blockDim.x) dst[c] = src[c];
 }
 }  // namespace
 
@@ -110,9 +111,9 @@ int rotate_rows_multi_f32(const RotateArgs* parts, int n, cudaStream_t st) {
 }
 
 int latent_rot_append_f32(const float* in, int64_t ld_in, const float* gamma, float* cache, const int32_t* row_slot, const int32_t* row_pos, int rows,
-                          int rank, int pairs, const float2* table, int Smax, float eps, cudaStream_t st) {
-    B2_CHECK_ARG(in && gamma && cache && row_slot && row_pos && rows > 0 && rank > 0 && pairs >= 0 && (pairs == 0 || table), "latent_rot_append: bad argument");
-    latent_rot_append_kernel<<<rows, 128, 0, st>>>(in, ld_in, gamma, cache, row_slot, row_pos, rank, pairs, table, Smax, eps);
+                          int rank, int rot, int pairs, const float2* table, int Smax, float eps, cudaStream_t st) {
+    B2_CHECK_ARG(in && gamma && cache && row_slot && row_pos && rows > 0 && rank > 0 && pairs >= 0 && 2 * pairs <= rot && (pairs == 0 || table), "latent_rot_append: bad argument");
+    latent_rot_append_kernel<<<rows, 128, 0, st>>>(in, ld_in, gamma, cache, row_slot, row_pos, rank, rot, pairs, table, Smax, eps);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -134,7 +135,7 @@ void rotary_frequencies(const RotaryDesc& d, std::vector<double>& freq, double& 
 }
 
 int rotary_table_build(const RotaryDesc& d, int positions, float2* table_dev) {
-    B2_CHECK_ARG(d.dims >= 2 && d.dims % 2 == 0 && d.base > 0.f && positions > 0 && table_dev, "rotary_table: bad argument");
+    B2_CHECK_ARG(d.dims >= 2 && d.base > 0.f && positions > 0 && table_dev, "rotary_table: bad argument");
     std::vector<double> freq;
     double mag;
     rotary_frequencies(d, freq, mag);

@@ -239,7 +239,7 @@ static int latent_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeight
         ldq = L.lqw_ld;
         B2_TRY(lin(proj, L.pproj_ld, W.uq_w, L.lqw, d.la_q_rank, q, ldq, R));
     }
-    if (own) B2_TRY(latent_rot_append_f32(proj + L.pq, L.pproj_ld, W.dkv_norm.as<float>(), S.lat.as<float>(), row_slot, row_pos, R, rank, pairs, tab,
+    if (own) B2_TRY(latent_rot_append_f32(proj + L.pq, L.pproj_ld, W.dkv_norm.as<float>(), S.lat.as<float>(), row_slot, row_pos, R, rank, rd, pairs, tab,
                                           kv->max_seq, eps, st));
     const float* gates = gate ? proj + L.pq + (own ? lrow : 0) : nullptr;
     float* lat_cache = KS.lat.as<float>();
@@ -1146,7 +1146,7 @@ int seq_kv_alloc(b2_kv* kv) {
                 cudaMemset(S.canon2.p, 0, n);
             }
         }
-        if (d.rot_dims > 0 && (d.type == B2_MIXER_GQA_ATTN || (d.type == B2_MIXER_LATENT_ATTN && d.la_rot_dim > 0))) {
+        if (d.rot_dims >= 2 && (d.type == B2_MIXER_GQA_ATTN || (d.type == B2_MIXER_LATENT_ATTN && d.la_rot_dim > 0))) {
             RotaryDesc rdesc;
             rdesc.dims = d.rot_dims; rdesc.base = d.rot_base; rdesc.factor = d.rot_factor; rdesc.original = d.rot_original; rdesc.fast = d.rot_fast;
             rdesc.slow = d.rot_slow;
@@ -1162,7 +1162,7 @@ int seq_kv_alloc(b2_kv* kv) {
                 B2_TRY(S.conv_tail.alloc(B * (d.ga_conv - 1) * L.conv_ch * F4));
                 cudaMemset(S.conv_tail.p, 0, S.conv_tail.bytes);
             }
-            if (d.ga_rot_values) {   // values turn over all of vdim with the plain frequencies of the same base
+            if (d.ga_rot_values && d.ga_vdim >= 2) {   // values turn over all of vdim (an odd last entry passes) with the plain frequencies of the same base
                 RotaryDesc vdesc;
                 vdesc.dims = d.ga_vdim; vdesc.base = d.rot_base;
                 B2_TRY(S.vrot_tab.alloc(Smax * (d.ga_vdim / 2) * sizeof(float2)));
@@ -1298,7 +1298,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             if (l.la_heads < 1 || l.la_dim < 1 || l.la_vdim < 1) why = "latent attention: heads and head sizes must be positive";
             else if (l.la_rot_dim < 0 || l.la_q_rank < 0 || l.la_kv_from < 0) why = "latent attention: negative size";
             else if (l.la_rank < 1 || l.la_rank > 512 || l.la_rank + l.la_rot_dim > 768) why = "latent attention: latent size 1..512, with the rotated part at most 768";
-            else if (l.la_rot_dim > 0 && (l.rot_dims < 2 || l.rot_dims % 2 || l.rot_dims > l.la_rot_dim || !(l.rot_base > 0.f))) why = "latent attention: an even number of rotated dimensions within the rotated part, positive base";
+            else if (l.la_rot_dim > 0 && (l.rot_dims < 1 || l.rot_dims > l.la_rot_dim || !(l.rot_base > 0.f))) why = "latent attention: rotated dimensions within the rotated part, positive base";
             else if (l.rot_factor > 0.f && !(l.rot_original > 0.f && l.rot_fast > 0.f && l.rot_slow > 0.f && l.rot_base > 1.f)) why = "rotation: scaled frequencies need original, fast and slow";
             else if (l.la_kv_from > 0) {
                 const int j = l.la_kv_from - 1;
@@ -1322,9 +1322,9 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             if (l.ga_heads < 1 || l.ga_kv_heads < 1 || l.ga_heads % l.ga_kv_heads) why = "attention: heads must be a positive multiple of kv_heads";
             else if (l.ga_dim < 1 || l.ga_dim > 512 || l.ga_vdim < 1 || l.ga_vdim > 512) why = "attention: head sizes 1..512";
             else if (l.ga_conv < 0 || l.ga_conv > 16) why = "attention: 0..16 convolution taps";
-            else if (l.rot_dims < 0 || l.rot_dims % 2 || l.rot_dims > l.ga_dim || (l.rot_dims > 0 && !(l.rot_base > 0.f))) why = "attention: an even number of rotated dimensions within a head, positive base";
+            else if (l.rot_dims < 0 || l.rot_dims > l.ga_dim || (l.rot_dims > 0 && !(l.rot_base > 0.f))) why = "attention: rotated dimensions within a head, positive base";
             else if (l.rot_factor > 0.f && !(l.rot_original > 0.f && l.rot_fast > 0.f && l.rot_slow > 0.f && l.rot_base > 1.f)) why = "rotation: scaled frequencies need original, fast and slow";
-            else if (l.ga_rot_values && (l.ga_vdim % 2 || !(l.rot_base > 0.f))) why = "attention: rotated values need an even vdim and a base";
+            else if (l.ga_rot_values && !(l.rot_base > 0.f)) why = "attention: rotated values need a base";
             else if (l.mask_kind < B2_MASK_CAUSAL || l.mask_kind > B2_MASK_CHUNK || (l.mask_kind != B2_MASK_CAUSAL && l.mask_size < 1)) why = "mask: unknown kind or empty size";
             L.nq = l.ga_heads * l.ga_dim; L.nk = l.ga_kv_heads * l.ga_dim; L.nv = l.ga_kv_heads * l.ga_vdim; L.ng = l.ga_heads * l.ga_vdim;
             L.lproj = L.nq + L.nk + L.nv + L.ng;

@@ -38,12 +38,12 @@ def grouped(heads, kv_heads, dim, vdim, conv, chunk, rot_dims, base=100.0, scali
 
 
 LAT = latent(3, 16, 8, 24, 40, 32, 7, scaling=YARN)
-LAT_ODD = latent(5, 9, 6, 7, 21, 11, 33, base=10000.0)                    # nothing a multiple of 4
+LAT_ODD = latent(5, 9, 7, 7, 21, 11, 33, base=10000.0)                    # nothing a multiple of 4, an odd rotated part (its last entry passes)
 LAT_ONE = latent(1, 16, 2, 16, 16, 16, 1)                                  # one head, one pair, a window that holds the query alone
 LAT_MANY = latent(40, 8, 4, 4, 24, 24, 50, scaling=YARN)                   # more heads than a CTA's pairs
 LAT_WIDE = latent(2, 32, 16, 48, 288, 64, 19)                              # cached rows wider than 256
 GQA = grouped(6, 2, 16, 24, 3, 11, 8, scaling=YARN)                        # part of a head rotated, keys with scaled frequencies
-GQA_ODD = grouped(2, 2, 7, 6, 0, 5, 4)                                     # groups of one head, no convolution, odd head size
+GQA_ODD = grouped(2, 2, 7, 9, 0, 5, 4)                                     # groups of one head, no convolution, odd head and value sizes
 GQA_TAP = grouped(3, 1, 8, 4, 1, 1, 2)                                     # a convolution of ONE tap, chunks of one position, one rotated pair
 GQA_ONE_KV = grouped(4, 1, 12, 10, 2, 64, 12, base=1.0e6)                  # one key/value head, all of a head rotated
 GQA_BIG = grouped(3, 3, 40, 136, 5, 29, 40)                                # values wider than 128
@@ -67,7 +67,7 @@ def config(layers, width=72, vocab=150, eps=1e-5, taps=3, logit_scale=0.7):
 
 
 CFG_MAIN = config([layer(LAT, MOE), layer(GQA, MOE_ALL), layer(latent(2, 24, 8, 8, 40, 16, 30, scaling=YARN, kv_from=0), None), layer(GQA_ONE_KV, MOE)], width=64)
-CFG_ODD = config([layer(GQA_ODD, MOE_ONE), layer(LAT_ODD, MOE_SINGLES), layer(latent(3, 5, 6, 9, 21, 7, 4, base=10000.0, kv_from=1), MOE_ONE)],
+CFG_ODD = config([layer(GQA_ODD, MOE_ONE), layer(LAT_ODD, MOE_SINGLES), layer(latent(3, 5, 7, 9, 21, 7, 4, base=10000.0, kv_from=1), MOE_ONE)],
                  width=50, vocab=77, eps=1e-3, taps=2, logit_scale=None)
 CFG_ONE_TAP = config([layer(LAT_ONE, None), layer(GQA_BIG, MOE_SINGLES), layer(LAT_MANY, None), layer(GQA_TAP, MOE_ONE)], width=48, taps=1, logit_scale=2.5)
 CFG_TAPS = config([layer(GQA_ONE_KV, None), layer(LAT_WIDE, MOE)], width=56, taps=6)
@@ -281,7 +281,7 @@ def with_mask(cfg, size):
     return out
 
 
-@pytest.mark.parametrize("kind,size", [("window", 37), ("window", 64), ("window", 300), ("chunk", 37), ("chunk", 96), ("chunk", 256)])
+@pytest.mark.parametrize("kind,size", [("window", 37), ("window", 64), ("window", 300), ("chunk", 37), ("chunk", 100), ("chunk", 256)])
 def test_keys_just_inside_and_outside_the_mask_and_far_away(kind, size):
     T = 420
     cfg, w = sharp_model(kind, size)
