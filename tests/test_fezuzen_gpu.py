@@ -443,3 +443,63 @@ def test_sampled_generation_repeats_with_the_seed_and_rejects_bad_input():
         model.generate(torch.tensor([[cfg["vocab"] + 3, 1, 2]]), max_new_tokens=2)
     with pytest.raises(ValueError):
         model.generate(p, max_new_tokens=4000)
+
+
+# ----------------------------------------------------------------------------------------------------------- the replay program
+def write_checkpoint(path, cfg, weights):
+    import json
+    import os
+    import struct
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    header, blobs, at = {}, [], 0
+    for k, v in weights.items():
+        raw = torch.from_numpy(np.asarray(v, np.float32)).bfloat16().contiguous().view(torch.int16).numpy().tobytes()
+        header[k] = {"dtype": "BF16", "shape": list(np.asarray(v).shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    with open(os.path.join(path, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program_on_a_written_checkpoint(dtype, tmp_path, repo_root):
+    """bin/trace_run on a checkpoint directory: two requests one after the other on slots that are given back, portions down to two
+    tokens, single tokens through the decode step, steps that want nothing; every written row against the oracle."""
+    import json
+    import subprocess
+    import sys
+
+    cfg = CFG_ODD
+    w = O.random_weights(cfg, seed=13)
+    write_checkpoint(str(tmp_path / "model"), cfg, w)
+    a, b = tokens_for(cfg, 60, seed=31), tokens_for(cfg, 23, seed=32)
+    steps, want_rows, at = [], [], 0
+    for n in (17, 2, 30, 2):                                                   # request a in portions, the last one asks for nothing
+        want = [] if n == 30 else list(range(0, n, 3))
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": a[at:at + n], "want": want}], "end": []})
+        want_rows.append(("a", [at + i for i in want]))
+        at += n
+    for t in range(at, len(a)):                                                # then token by token
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [a[t]], "want": [0]}], "end": ["a"] if t == len(a) - 1 else []})
+        want_rows.append(("a", [t]))
+    steps.append({"step": len(steps), "entries": [{"id": "b", "tokens": b, "want": [0, len(b) - 1]}], "end": ["b"]})
+    want_rows.append(("b", [0, len(b) - 1]))
+    out = tmp_path / "out"
+    run = subprocess.run([sys.executable, f"{repo_root}/bin/trace_run", "--model", str(tmp_path / "model"), "--dtype", dtype, "--out", str(out),
+                          "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert [ln for ln in run.stdout.splitlines() if ln.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    ref = {"a": O.forward(cfg, w, a), "b": O.forward(cfg, w, b)}
+    got, exp = [], []
+    for i, (rid, rows) in enumerate(want_rows):
+        path = out / f"{i}.f32"
+        if not rows:
+            assert not path.exists()
+            continue
+        got.append(np.fromfile(path, dtype="<f4").reshape(len(rows), cfg["vocab"]))
+        exp.append(ref[rid][rows])
+    assert close(torch.from_numpy(np.concatenate(got)), np.concatenate(exp), torch.float32 if dtype == "float32" else torch.bfloat16)
