@@ -205,8 +205,19 @@ int b2_batch_set_row(b2_model* m, b2_kv* kv, int slot, int active, const b2_samp
  *                      a short causal depthwise convolution over time on q, k and v, rotary positions on q and k (rot_*),
  *                      optionally values rotated by their own position over all of vdim and the head's output turned back by
  *                      the query's position (ga_rot_values), ga_sink != 0: one extra term exp(ga_sink_value) in the softmax
- *                      denominator; mask_* limits the visible keys
- * Visible keys (mask_kind): B2_MASK_CAUSAL all j <= i; B2_MASK_WINDOW 0 <= i - j < mask_size; B2_MASK_CHUNK j <= i with
+ *                      denominator; mask_* limits the visible keys.
+ *                      Options (zero = the form above): ga_gate chooses the output gate (per channel, ONE sigmoid per head, or
+ *                      none); ga_qk_norm norms every query and key head with a weight vector shared by the heads (before
+ *                      the rotation); ga_rot_half pairs entry m with entry m + rot_dims / 2 instead of its neighbour;
+ *                      ga_maps == 2 is differential attention: every query and key head holds TWO maps of ga_dim entries
+ *                      each ([map 1 | map 2], the convolution and the rotation act on each), both attend over the same
+ *                      values, and a head's output is unit_rms(a1 - lambda a2) * (1 - ga_diff) with ONE learned number
+ *                      lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ga_diff for the layer
+ *   B2_MIXER_GLA       gated linear attention: S <- diag(alpha) S + k v^T, o = S^T q with q = W_q h * dim^(-1/2) and a decay per
+ *                      key channel alpha = sigmoid(W_a2 (W_a1 h) + b)^(1 / gl_tau) through a low-rank pair of matrices; per-head
+ *                      RMS norm with one weight vector for all heads, SiLU(W_g h) gate, out-projection
+ * Visible keys (mask_kind): B2_MASK_CAUSAL all j <= i; B2_MASK_WINDOW 0 <= i - j < mask_size, and with mask_keep > 0 also the
+ * sequence's first mask_keep positions whatever their distance; B2_MASK_CHUNK j <= i with
  * floor(i / mask_size) == floor(j / mask_size), chunks counted from position 0 of the sequence.
  * Rotation (rot_*): pairs (2m, 2m+1), m < rot_dims / 2, of a head turn by p * f_m, f_m = rot_base^(-2m / rot_dims); with
  * rot_factor > 0 the frequencies are blended towards f_m / rot_factor over the pairs whose wavelength lies between
@@ -215,24 +226,28 @@ int b2_batch_set_row(b2_model* m, b2_kv* kv, int slot, int active, const b2_samp
  * x += residual_mult * sublayer(g * unit_rms(x)) with ONE learned number g per norm (also in front of the head);
  * B2_BLOCK_SANDWICH_RMS norms both sides with weighted RMS norms, x += rms_w'(sublayer(u + conv(u))), u = rms_w(x), where
  * conv is a causal depthwise convolution over time of input_conv_taps taps (0: none; 1: a factor per channel) whose last taps - 1 inputs are carried
- * per slot, for the mixer and for the feed-forward of every layer.
- * Feed-forwards: B2_FF_RELU_SQ (W_down relu(W_up x)^2), B2_FF_POLYNORM (biased projections around
+ * per slot, for the mixer and for the feed-forward of every layer; B2_BLOCK_PARALLEL_RMS has ONE weighted RMS norm per layer
+ * that both sublayers read: x += residual_mult * (mixer(u) + ff(u)), u = rms_w(x).
+ * Feed-forwards: B2_FF_CLAMP_GLU (W_down (a(g) (u + 1)) with g = min(W_gate x, ff_limit), u = clamp(W_up x, +-ff_limit),
+ * a(g) = g sigmoid(ff_act_slope g)), B2_FF_RELU_SQ (W_down relu(W_up x)^2), B2_FF_POLYNORM (biased projections around
  * a N(z) + b N(z^2) + c N(z^3) + e, N = division by the token's root mean square), B2_FF_MOE (router, group-limited
  * top-k, experts without biases, optional shared expert; moe_score: sigmoid or softmax scores; moe_group_score: a group counts
  * by its two best experts or by its best; moe_raw_weights: the chosen scores are the weights as they are, else divided by their
  * sum and scaled; moe_act: SiLU-gated experts or W_down relu(W_up x)^2).
  * A model may add a hashed bigram row to every token embedding, loop a block of layers several times with the same tensors
  * (every pass has its own cache/state; before a pass the embedding output is added again from the second pass on, and a
- * learned per-pass vector always), and soft-cap its logits with tanh.
+ * learned per-pass vector always; loop_plain: nothing is added between the passes), scale its token embedding, and soft-cap its
+ * logits with tanh.
  * The reference has no such models (its LLMs are HF LLaMA / MPT, llava/model/language_model/); what is shared with the
  * LLaVA path is everything around the layers: b2_kv slots and lengths, b2_decode_step / b2_decode_greedy / b2_stream_* /
  * b2_batch_* (CUDA-graph decode step, device-side token selection, host token ring, continuous batching).
  * compute: B2_COMPUTE_BF16 = bf16 x bf16 -> fp32 matrix products on bf16 weights, everything else fp32;
  *          B2_COMPUTE_F32  = true fp32 throughout (weights widened at load, FMA products, no TF32). */
 enum { B2_ARCH_LLAVA = 0, B2_ARCH_LAYER_LIST = 1 };
-enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2, B2_MIXER_LATENT_ATTN = 3, B2_MIXER_HGRN2 = 4, B2_MIXER_GQA_ATTN = 5 };
-enum { B2_FF_RELU_SQ = 0, B2_FF_POLYNORM = 1, B2_FF_MOE = 2 };
-enum { B2_BLOCK_POST_LN = 0, B2_BLOCK_PRE_RMS1 = 1, B2_BLOCK_SANDWICH_RMS = 2 };
+enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2, B2_MIXER_LATENT_ATTN = 3, B2_MIXER_HGRN2 = 4, B2_MIXER_GQA_ATTN = 5, B2_MIXER_GLA = 6 };
+enum { B2_FF_RELU_SQ = 0, B2_FF_POLYNORM = 1, B2_FF_MOE = 2, B2_FF_CLAMP_GLU = 3 };
+enum { B2_BLOCK_POST_LN = 0, B2_BLOCK_PRE_RMS1 = 1, B2_BLOCK_SANDWICH_RMS = 2, B2_BLOCK_PARALLEL_RMS = 3 };
+enum { B2_GATE_CHANNEL = 0, B2_GATE_HEAD = 1, B2_GATE_NONE = 2 };
 enum { B2_MASK_CAUSAL = 0, B2_MASK_WINDOW = 1, B2_MASK_CHUNK = 2 };
 enum { B2_MOE_SCORE_SIGMOID = 0, B2_MOE_SCORE_SOFTMAX = 1 };
 enum { B2_MOE_GROUP_TOP2_SUM = 0, B2_MOE_GROUP_MAX = 1 };
@@ -273,6 +288,18 @@ typedef struct b2_seq_layer_desc {
     int32_t mask_kind, mask_size;   /* B2_MASK_* */
     int32_t rot_dims;               /* rotated leading dimensions of a head (of the rotated part, for latent attention); an odd last one passes */
     float rot_base, rot_factor, rot_original, rot_fast, rot_slow;   /* rot_factor 0: plain frequencies */
+    /* B2_MIXER_GQA_ATTN, further forms (zero: one map, no q / k norm, neighbouring pairs, a gate per channel) */
+    int32_t ga_maps;         /* 2: differential attention (two maps per head over the same values); 0 or 1: one map */
+    float ga_diff;           /* ga_maps == 2: the constant of lambda, and 1 - ga_diff scales the head's output */
+    int32_t ga_qk_norm;      /* weighted RMS norm of every query and key head (weights shared by the heads) before the rotation */
+    int32_t ga_rot_half;     /* rotated pairs are (m, m + rot_dims / 2) */
+    int32_t ga_gate;         /* B2_GATE_* */
+    int32_t mask_keep;       /* B2_MASK_WINDOW: the first mask_keep positions of a sequence stay visible */
+    /* B2_MIXER_GLA */
+    int32_t gl_heads, gl_dim, gl_vdim, gl_rank;   /* gl_rank: inner size of the low-rank decay projection */
+    float gl_tau;
+    /* B2_FF_CLAMP_GLU */
+    float ff_limit, ff_act_slope;
 } b2_seq_layer_desc;
 typedef struct b2_seq_model_desc {
     int32_t width, vocab, n_layers;
@@ -288,6 +315,8 @@ typedef struct b2_seq_model_desc {
     int32_t loop_start, loop_stop, loop_times;                /* layers [start, stop) run `times` times in a row; times 0: no loop */
     float logit_scale;       /* factor on the logits; 0 = 1 */
     int32_t input_conv_taps; /* B2_BLOCK_SANDWICH_RMS: taps of the convolution every sublayer's input passes (0: none) */
+    float embed_scale;       /* factor on the token embedding; 0 = 1 */
+    int32_t loop_plain;      /* the passes of the looped block follow one another with nothing added in between (no loop.step tensor) */
 } b2_seq_model_desc;
 int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* layers, b2_model** out);
 /* Layer RUNS of one forward pass (a looped layer counts every time): rows of b2_append_tokens' resid_out; -1 for other models */
@@ -300,7 +329,10 @@ int b2_seq_model_runs(const b2_model* m);
  * l<i>.mlp.{up,up.b,down,down.b,act} (PolyNorm), l<i>.mlp.{router,e<j>.gate,e<j>.up,e<j>.down,shared.gate,shared.up,shared.down}.
  * B2_BLOCK_SANDWICH_RMS models: embed, head, final.norm, l<i>.{norm1,norm1b,norm2,norm2b} (width each), l<i>.{canon1,canon2}
  * ([width, taps]), l<i>.mix.{dq,dq.norm,uq,dkv,dkv.norm,uk,uv,o} (latent attention; no dkv* with la_kv_from),
- * l<i>.mix.{q,k,v,q.conv,k.conv,v.conv,g,o} (grouped attention), l<i>.mlp.{router,e<j>.up,e<j>.down,shared.up,shared.down}. */
+ * l<i>.mix.{q,k,v,q.conv,k.conv,v.conv,g,o} (grouped attention), l<i>.mlp.{router,e<j>.up,e<j>.down,shared.up,shared.down}.
+ * B2_BLOCK_PARALLEL_RMS models: embed, head, final.norm, l<i>.norm1 (width each), l<i>.mix.{q,k,v,o} with, by the layer's options,
+ * {q,k,v}.conv, {q,k}.norm, g, {lq1,lk1,lq2,lk2} (grouped attention), l<i>.mix.{q,k,v,g,a1,a2,a2.b,norm,o} (gated linear attention),
+ * l<i>.mlp.{gate,up,down}. */
 /* Feed the next n tokens of the request in cache slot `slot` (a portion of its prompt, or all of it): the slot's state and
  * key/value rows continue from its current length, or from an empty sequence when restart != 0 (whatever the slot held
  * is then dead: nothing needs clearing). want_host lists n_want indices into these n tokens whose logits are written to

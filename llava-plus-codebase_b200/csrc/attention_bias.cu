@@ -9,7 +9,10 @@
 // kcache == vcache, dk == dv <= 512, G = 1), without bias table or soft-cap (rel == null), and with a per-head sink: one
 // extra term exp(sink[h]) in the softmax denominator that has no key and no value (or exp(sink_value) for every head). A cached
 // row may be longer than the value it holds (dv < dk: a latent followed by a rotated key part). The visible keys of a row may be
-// limited to a sliding window or to the row's chunk of positions: keys in front of the first visible one are never loaded.
+// limited to a sliding window or to the row's chunk of positions: keys in front of the first visible one are never loaded. A
+// window may keep the sequence's first positions visible (mask_keep): the visible keys are then two ranges, [0, keep) and the
+// window, and the tiles of the gap between them are never staged. Value heads may be fewer than key heads (Gv < G: key head g
+// reads value head g mod Gv), which is how the two maps of differential attention share one set of values.
 #include <math.h>
 
 #include "common.cuh"
@@ -84,17 +87,24 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
     __syncwarp();
     const float* K = a.kcache + ((size_t)slot * a.G + g) * a.Smax * a.dk;
     const size_t vrs = a.vcache == a.kcache ? (size_t)a.dk : (size_t)a.dv;   // keys that hold the value: the key row's pitch
-    const float* V = a.vcache + ((size_t)slot * a.G + g) * a.Smax * vrs;
-    int lo = mask_first(pos, a.mask_kind, a.mask_size), hi = pos + 1;
+    const int Gv = a.Gv > 0 ? a.Gv : a.G;
+    const float* V = a.vcache + ((size_t)slot * Gv + g % Gv) * a.Smax * vrs;
+    // visible keys: [0, nA) (the kept first positions in front of the window; empty without them) and [first, pos], walked as
+    // tiles of 32 that the key splits share out
+    const int first = mask_first(pos, a.mask_kind, a.mask_size);
+    const int nA = a.mask_kind == MASK_WINDOW ? min(a.mask_keep, first) : 0, tilesA = (nA + 31) / 32;
+    const int T = tilesA + (pos + 1 - first + 31) / 32;
+    int t_lo = 0, t_hi = T;
     if (a.nsplit > 1) {
-        const int per = ((hi - lo + a.nsplit - 1) / a.nsplit + 31) / 32 * 32;
-        lo += sp * per;
-        hi = min(pos + 1, lo + per);
+        const int per = (T + a.nsplit - 1) / a.nsplit;
+        t_lo = sp * per;
+        t_hi = min(T, t_lo + per);
     }
     float m = -INFINITY, l = 0.f, o[AT_MAXC];
 #pragma unroll
     for (int c = 0; c < AT_MAXC; ++c) o[c] = 0.f;
-    for (int j0 = lo; j0 < hi; j0 += 32) {
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int j0 = t < tilesA ? t * 32 : first + (t - tilesA) * 32, hi = t < tilesA ? nA : pos + 1;
         const int j = j0 + lane;
         const bool valid = j < hi;
         float s = -INFINITY;
@@ -202,13 +212,14 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
     const float* sVal = shared_kv ? sK : sV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int slot = a.row_slot[r0];
-    int maxpos = -1, first = 0x7fffffff;   // last and first key position any row of the tile sees
+    int maxpos = -1, first = 0x7fffffff;   // last and first key position any row of the tile sees (kept first positions aside)
     for (int i = 0; i < nrows; ++i) {
         const int p = a.row_pos[r0 + i];
         maxpos = max(maxpos, p);
         if (p >= 0) first = min(first, mask_first(p, a.mask_kind, a.mask_size));
     }
     if (maxpos < 0) return;
+    const int keep = a.mask_kind == MASK_WINDOW ? a.mask_keep : 0;
     if (VEC && a.ldq % 4 == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0) {
         // a row's heads of this chunk are consecutive in q: HG * dk floats per row, copied 16 bytes at a time
         for (int i = 0; i < nrows; ++i)
@@ -219,17 +230,23 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
             sQ[e] = a.q[(size_t)(r0 + p / HG) * a.ldq + (size_t)(h0 + p % HG) * dk + d];
         }
     }
-    int lo = first, hi = maxpos + 1;
+    // The keys the tile's rows see are two ranges: [0, nA), the kept first positions in front of the earliest window (empty without
+    // them), and [first, maxpos]. They are walked as tiles of TL_KT keys, none of which straddles the gap, and the key splits of a
+    // decode step share out the tiles.
+    const int nA = min(keep, first), tilesA = (nA + TL_KT - 1) / TL_KT;
+    const int T = tilesA + (maxpos + 1 - first + TL_KT - 1) / TL_KT;
+    int t_lo = 0, t_hi = T;
     if (a.nsplit > 1) {
-        const int per = ((hi - lo + a.nsplit - 1) / a.nsplit + TL_KT - 1) / TL_KT * TL_KT;
-        lo += sp * per;
-        hi = min(maxpos + 1, lo + per);
+        const int per = (T + a.nsplit - 1) / a.nsplit;
+        t_lo = sp * per;
+        t_hi = min(T, t_lo + per);
     }
     // cache slabs [slot][head][position][size], or (kv_row_stride > 0) one matrix [position][head * size] made for this call
     const bool mat = a.kv_row_stride > 0;
+    const int Gv = a.Gv > 0 ? a.Gv : a.G, gv = g % Gv;   // fewer value heads than key heads: key head g reads value head g mod Gv
     const size_t krs = mat ? (size_t)a.kv_row_stride : (size_t)dk, vrs = mat ? (size_t)a.kv_row_stride_v : (size_t)dv;
     const float* K = mat ? a.kcache + (size_t)g * dk : a.kcache + ((size_t)slot * a.G + g) * a.Smax * dk;
-    const float* V = mat ? a.vcache + (size_t)g * dv : a.vcache + ((size_t)slot * a.G + g) * a.Smax * dv;
+    const float* V = mat ? a.vcache + (size_t)gv * dv : a.vcache + ((size_t)slot * Gv + gv) * a.Smax * dv;
     const bool vecv = VEC && dv % 4 == 0 && vrs % 4 == 0 && (reinterpret_cast<uintptr_t>(V) & 15) == 0;   // 16-byte value rows
     float m[TL_PPW], l[TL_PPW], o[TL_PPW][MAXC];
     int ppos[TL_PPW], pfirst[TL_PPW];
@@ -242,8 +259,10 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
 #pragma unroll
         for (int c = 0; c < MAXC; ++c) o[i][c] = 0.f;
     }
-    for (int j0 = lo; j0 < hi; j0 += TL_KT) {
-        const int nk = min(TL_KT, hi - j0);
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int j0 = t < tilesA ? t * TL_KT : first + (t - tilesA) * TL_KT;
+        const int nk = min(TL_KT, (t < tilesA ? nA : maxpos + 1) - j0);
+        const bool kept = j0 < keep;   // the tile holds kept first positions: visible to every row behind them, whatever its window
         __syncthreads();
         if (VEC) {
             copy_rows_f4<4>(sK, dkp, K + (size_t)j0 * krs, krs, nk, dk >> 2, tid);
@@ -267,7 +286,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
                     const float4 kv = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
                     for (int i = 0; i < TL_PPW; ++i) {
-                        if (ppos[i] >= j0 && pfirst[i] < j0 + nk) {   // idle pairs and pairs whose keys all lie ahead or behind skip (warp-uniform)
+                        if (ppos[i] >= j0 && (kept || pfirst[i] < j0 + nk)) {   // idle pairs and pairs whose keys all lie ahead or behind skip (warp-uniform)
                             const float4 qv = *reinterpret_cast<const float4*>(sQ + (warp + TL_WARPS * i) * dk + d);
                             sc[i] = fmaf(qv.x, kv.x, sc[i]); sc[i] = fmaf(qv.y, kv.y, sc[i]);
                             sc[i] = fmaf(qv.z, kv.z, sc[i]); sc[i] = fmaf(qv.w, kv.w, sc[i]);
@@ -279,7 +298,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
                     const float kv = kr[d];
 #pragma unroll
                     for (int i = 0; i < TL_PPW; ++i)
-                        if (ppos[i] >= j0 && pfirst[i] < j0 + nk) sc[i] = fmaf(sQ[(warp + TL_WARPS * i) * dk + d], kv, sc[i]);
+                        if (ppos[i] >= j0 && (kept || pfirst[i] < j0 + nk)) sc[i] = fmaf(sQ[(warp + TL_WARPS * i) * dk + d], kv, sc[i]);
                 }
             }
         }
@@ -289,11 +308,11 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
         for (int i = 0; i < TL_PPW; ++i) {
             pr[i] = 0.f;
             const int pos = ppos[i];
-            if (pos < j0 || pfirst[i] >= j0 + nk) continue;   // no key of this tile is visible: the running maximum stays as it is
+            if (pos < j0 || (!kept && pfirst[i] >= j0 + nk)) continue;   // no key of this tile is visible: the running maximum stays as it is
             any = true;
             const int head = h0 + (warp + TL_WARPS * i) % HG;
             const int j = j0 + lane;
-            const bool valid = lane < nk && j <= pos && j >= pfirst[i];
+            const bool valid = lane < nk && j <= pos && (j >= pfirst[i] || j < keep);
             float sv = -INFINITY;
             if (valid) {
                 sv = sc[i] * a.scale;
@@ -405,6 +424,8 @@ int check_args(const BiasAttnArgs& a, const char* who) {
     B2_CHECK_ARG(a.dk > 0 && a.dk <= 768 && a.dv > 0 && a.dv <= 512, "%s: head sizes %d / %d exceed 768 / 512", who, a.dk, a.dv);
     B2_CHECK_ARG(a.vcache != a.kcache || a.dv <= a.dk, "%s: keys that also hold the values need dv <= dk", who);
     B2_CHECK_ARG(a.mask_kind == MASK_CAUSAL || ((a.mask_kind == MASK_WINDOW || a.mask_kind == MASK_CHUNK) && a.mask_size >= 1), "%s: mask %d of size %d", who, a.mask_kind, a.mask_size);
+    B2_CHECK_ARG(a.mask_keep >= 0 && (a.mask_keep == 0 || a.mask_kind == MASK_WINDOW), "%s: kept first positions belong to a window", who);
+    B2_CHECK_ARG(a.Gv >= 0 && (a.Gv == 0 || (a.G % a.Gv == 0 && a.vcache != a.kcache && a.kv_row_stride == 0)), "%s: %d key heads cannot share %d value heads", who, a.G, a.Gv);
     B2_CHECK_ARG(a.kv_row_stride == 0 || (a.kv_row_stride_v > 0 && a.tile_rows >= 1 && a.vcache != a.kcache), "%s: key/value matrices need both pitches and the tiled kernel", who);
     return 0;
 }

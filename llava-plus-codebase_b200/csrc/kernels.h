@@ -302,6 +302,7 @@ struct GroupedLinearArgs {
     int act = LIN_NONE;
     int round_a = 0;
     int swiglu = 0;   // one-row tiles only: a group's matrix is [gate | up] of N rows each and out[m, n] = silu(gate_n . a) * (up_n . a)
+    float glu_slope = 1.f, glu_limit = 0.f, glu_up_shift = 0.f;   // with swiglu: the general gated unit (GluAct) instead of SiLU(g) u
 };
 int linear_grouped_f32(const GroupedLinearArgs& g, cudaStream_t stream);
 // `batch` small Linears in one launch on a handful of rows (a decode step's per-head products): for b < batch,
@@ -334,6 +335,15 @@ int moe_plan(const int32_t* idx, int rows, int top, int experts, int tile, int m
 // tensor-core product reads next (out may then be null)
 int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t stream, void* out16 = nullptr,
                     int64_t ld_out16 = 0);
+// The gated unit in its general form: with g = in[r, c] and u = in[r, ff + c], limit > 0 first bounds them, g = min(g, limit),
+// u = clamp(u, -limit, limit); out = g sigmoid(slope g) (u + up_shift). (slope 1, no limit, shift 0: SiLU(g) u.)
+struct GluAct { float slope = 1.f, limit = 0.f, up_shift = 0.f; };
+__host__ __device__ inline float glu_act(float g, float u, const GluAct& a) {
+    if (a.limit > 0.f) { g = fminf(g, a.limit); u = fminf(fmaxf(u, -a.limit), a.limit); }
+    return g / (1.f + expf(-a.slope * g)) * (u + a.up_shift);
+}
+int glu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, const GluAct& act, cudaStream_t stream,
+                 void* out16 = nullptr, int64_t ld_out16 = 0);
 // out[p, :K] = bf16(A[src_row[p], :K]), zeros where src_row[p] < 0: the gathered A operand of a grouped tensor-core product
 int gather_rows_bf16(const float* A, int64_t lda, const int32_t* src_row, void* out, int64_t ld_out, int rows, int K, cudaStream_t stream);
 // x[r] += alpha * sum_k w[r, k] * y[pair_pos[r * top + k]] (pair_pos null: the pair's own index)
@@ -349,8 +359,9 @@ int layernorm_gather_f32(const float* x, const int32_t* row_index, const float* 
 // Per row and per group of `group` consecutive channels (cols % group == 0):
 //   gate_first: out = unit_rms(y * silu(z)) * gamma            (state-space mixer: the gate comes before the norm)
 //   otherwise : out = unit_rms(y) * gamma * silu(z)            (RWKV mixer: per-head norm, then weight, then gate)
+// gamma_shared: one weight vector [group] for every group instead of [cols]
 int gated_group_rmsnorm_f32(const float* y, int64_t ldy, const float* z, int64_t ldz, const float* gamma, float* out, int64_t ldo, int rows,
-                            int cols, int group, int gate_first, float eps, cudaStream_t stream);
+                            int cols, int group, int gate_first, float eps, cudaStream_t stream, int gamma_shared = 0);
 // ungated form; gamma_shared: one weight vector [group] for every group instead of [cols]
 int group_rmsnorm_f32(const float* y, int64_t ldy, const float* gamma, int gamma_shared, float* out, int64_t ldo, int rows, int cols, int group,
                       float eps, cudaStream_t stream);
@@ -378,7 +389,11 @@ int latent_append_f32(const float* in, int64_t ld_in, const float* gamma, float*
                       int rank, int Smax, float eps, cudaStream_t stream);
 // x[r, :] = table[tokens[r], :] as fp32; ids outside [0, vocab) give a zero row and raise *err_flag (B2_ERR_TOKEN_RANGE)
 int embed_rows_f32(const int32_t* tokens, const void* table, int table_dtype, float* x, int rows, int cols, int vocab, int* err_flag,
-                   cudaStream_t stream);
+                   cudaStream_t stream, float scale = 1.f);   // scale: x = table[token] * scale, in fp32
+// Differential attention, per (row, head): d = a1 - lambda a2 over the head's dv values, out = d / sqrt(mean(d^2) + eps) * out_scale.
+// y holds map 1 of every head, then map 2 of every head: [rows, 2 * heads * dv]
+int diff_combine_f32(const float* y, int64_t ldy, float* out, int64_t ldo, int rows, int heads, int dv, float lambda, float out_scale, float eps,
+                     cudaStream_t stream);
 // out[r, c] = a[r, c] * sigmoid(g[r, c])
 int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, float* out, int64_t ldo, int rows, int cols, cudaStream_t stream);
 
@@ -402,7 +417,7 @@ struct SandwichNormArgs {
 int sandwich_norm_f32(const SandwichNormArgs& a, cudaStream_t stream);
 
 // ---- rotary positions (rotary.cu) -------------------------------------------------------------------------------------------
-// Pairs (2m, 2m+1), m < floor(dims / 2), turn by position * f_m, f_m = base^(-2m / dims). factor > 0: f_m is blended towards f_m / factor
+// Pairs (2m, 2m+1) (or, in the half layout, (m, m + pairs)), m < floor(dims / 2), turn by position * f_m, f_m = base^(-2m / dims). factor > 0: f_m is blended towards f_m / factor
 // over the pairs between lo = max(floor(dim(fast)), 0) and hi = min(ceil(dim(slow)), dims - 1), dim(t) = dims ln(original / (2 pi t)) /
 // (2 ln base), and cos / sin are scaled by 0.1 ln(factor) + 1.
 struct RotaryDesc { int dims = 0; float base = 10000.f, factor = 0.f, original = 0.f, fast = 0.f, slow = 0.f; };
@@ -420,6 +435,9 @@ struct RotateArgs {
     const float2* table = nullptr;               // [positions][pairs]
     int heads = 0, size = 0, offset = 0, pairs = 0, inverse = 0, rows = 0;
     const int32_t* row_slot = nullptr; const int32_t* row_pos = nullptr;
+    int half = 0;                                // pair m is (offset + m, offset + m + pairs) instead of (offset + 2m, offset + 2m + 1)
+    const float* norm_w = nullptr; float eps = 0.f;   // non-null: the head is first normed, x / sqrt(mean(x^2) + eps) * norm_w over its `size` entries
+                                                      // (one weight vector for all heads); such calls run one warp per (row, head)
 };
 int rotate_rows_f32(const RotateArgs& a, cudaStream_t stream);
 // up to three such calls over the same rows in one launch (queries, keys and values of an attention layer)
@@ -451,14 +469,17 @@ int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out
 //   SCAN_RWKV: y = (S + diag(bonus[h]) k v^T)^T q ; S = diag(exp(-exp(w_log))) S + k v^T    (q, k, w_log: [rows, heads, dk])
 //   SCAN_HGRN2: f = l + (1 - l) sigmoid(z + b) per key channel; S = diag(f) S + (1 - f) v^T ; y = S^T silu(q)   (q, z: [rows, heads, dk]
 //              raw projections; l, b: [heads, dk]; there is no key input: what the gate forgets is what it writes)
-enum { SCAN_SSD = 0, SCAN_RWKV = 1, SCAN_HGRN2 = 2 };
+//   SCAN_GLA : alpha = sigmoid(z + b)^(1 / tau) per key channel; S = diag(alpha) S + k v^T ; y = S^T (q_scale q)   (q, k, z: [rows, heads, dk];
+//              b: [heads, dk] in gate_bias)
+enum { SCAN_SSD = 0, SCAN_RWKV = 1, SCAN_HGRN2 = 2, SCAN_GLA = 3 };
 struct ScanArgs {
     int mode = SCAN_SSD;
     const float *q = nullptr, *k = nullptr, *v = nullptr; int64_t ldq = 0, ldk = 0, ldv = 0;
-    const float* decay_in = nullptr; int64_t ldd = 0;  // SSD: dt_raw [rows, heads]; RWKV: w_log [rows, heads*dk]; HGRN2: z [rows, heads*dk]
-    const float *gate_bias = nullptr, *gate_lower = nullptr;              // HGRN2, [heads, dk]
+    const float* decay_in = nullptr; int64_t ldd = 0;  // SSD: dt_raw [rows, heads]; RWKV: w_log [rows, heads*dk]; HGRN2, GLA: z [rows, heads*dk]
+    const float *gate_bias = nullptr, *gate_lower = nullptr;              // HGRN2 (GLA: gate_bias alone), [heads, dk]
     const float *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr;  // SSD, [heads]
     const float* bonus = nullptr;                                         // RWKV, [heads, dk]
+    float q_scale = 1.f, tau = 1.f;                                       // GLA
     float* state = nullptr;                                               // [slots][heads][dk][dv]
     float* y = nullptr; int64_t ldy = 0;                                  // [rows, heads*dv]
     int heads = 0, groups = 0, dk = 0, dv = 0;
@@ -487,6 +508,9 @@ struct BiasAttnArgs {
     int sink_fixed = 0; float sink_value = 0.f;   // sink_fixed (with sink null): exp(sink_value) does, for every head
     int mask_kind = 0, mask_size = 0;             // MASK_* (the values of B2_MASK_*): row at position i sees j <= i (causal), and only i - j < size (window) or
                                                   // floor(i / size) == floor(j / size) (chunk)
+    int mask_keep = 0;                            // MASK_WINDOW: positions j < mask_keep stay visible whatever their distance
+    int Gv = 0;                                   // > 0: vcache holds Gv <= G value heads per slot and key head g reads value head g mod Gv
+                                                  // (the maps of differential attention: G = maps * Gv key heads over one set of values)
     float* partial = nullptr; int nsplit = 1;     // split-KV scratch [rows*H*nsplit*(dv+2)] when nsplit > 1
     int tile_rows = 0;                            // consecutive rows that share a slot (a prompt portion: its rows; a decode step: 1);
                                                   // 0: one warp per (row, head) without shared key/value tiles

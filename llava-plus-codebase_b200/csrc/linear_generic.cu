@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(256) linear_grouped_rows_kernel(GroupedLinearA
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xffffffffu, acc, o); acc2 += __shfl_xor_sync(0xffffffffu, acc2, o); }
     if (lane == 0) {
-        if (g.swiglu) g.out[(size_t)m * g.ld_out + n] = acc / (1.f + expf(-acc)) * acc2;   // silu(gate) * up
+        if (g.swiglu) g.out[(size_t)m * g.ld_out + n] = glu_act(acc, acc2, GluAct{g.glu_slope, g.glu_limit, g.glu_up_shift});   // silu(gate) * up, or its bounded form
         else lin_store(g.out + (size_t)m * g.ld_out + n, acc, nullptr, n, g.act, 1.f, 0);
     }
 }

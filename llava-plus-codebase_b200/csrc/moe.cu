@@ -123,14 +123,13 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int32_t* __restric
     }
 }
 
-// out[r, c] = silu(in[r, c]) * in[r, ff + c]
-__global__ void swiglu_rows_kernel(const float* __restrict__ in, int64_t ld_in, float* __restrict__ out, int64_t ld_out, int ff,
-                                   __nv_bfloat16* __restrict__ out16, int64_t ld_out16) {
+// out[r, c] = act(in[r, c], in[r, ff + c]): the gated unit (SiLU(g) u, or its bounded and shifted form)
+__global__ void glu_rows_kernel(const float* __restrict__ in, int64_t ld_in, float* __restrict__ out, int64_t ld_out, int ff,
+                                __nv_bfloat16* __restrict__ out16, int64_t ld_out16, GluAct act) {
     const size_t r = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c < ff) {
-        const float g = in[r * ld_in + c];
-        const float v = g / (1.f + expf(-g)) * in[r * ld_in + ff + c];
+        const float v = glu_act(in[r * ld_in + c], in[r * ld_in + ff + c], act);
         if (out != nullptr) out[r * ld_out + c] = v;
         if (out16 != nullptr) out16[r * ld_out16 + c] = __float2bfloat16_rn(v);
     }
@@ -187,11 +186,16 @@ int moe_plan(const int32_t* idx, int rows, int top, int experts, int tile, int m
     return 0;
 }
 
-int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t st, void* out16, int64_t ld_out16) {
-    B2_CHECK_ARG(in && (out || out16) && rows > 0 && ff > 0, "swiglu_rows: bad argument");
-    swiglu_rows_kernel<<<dim3((ff + 255) / 256, rows), 256, 0, st>>>(in, ld_in, out, ld_out, ff, reinterpret_cast<__nv_bfloat16*>(out16), ld_out16);
+int glu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, const GluAct& act, cudaStream_t st, void* out16,
+                 int64_t ld_out16) {
+    B2_CHECK_ARG(in && (out || out16) && rows > 0 && ff > 0, "glu_rows: bad argument");
+    glu_rows_kernel<<<dim3((ff + 255) / 256, rows), 256, 0, st>>>(in, ld_in, out, ld_out, ff, reinterpret_cast<__nv_bfloat16*>(out16), ld_out16, act);
     B2_LAUNCH_CHECK();
     return 0;
+}
+
+int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t st, void* out16, int64_t ld_out16) {
+    return glu_rows_f32(in, ld_in, out, ld_out, rows, ff, GluAct{}, st, out16, ld_out16);
 }
 
 int gather_rows_bf16(const float* A, int64_t lda, const int32_t* src_row, void* out, int64_t ld_out, int rows, int K, cudaStream_t st) {

@@ -87,14 +87,34 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, int64_t 
     }
 }
 
+// differential attention: one warp per (row, head) subtracts lambda times the second map's output from the first map's and brings
+// the difference to unit RMS
+__global__ void diff_combine_kernel(const float* __restrict__ y, int64_t ldy, float* __restrict__ out, int64_t ldo, int rows, int heads, int dv,
+                                    float lambda, float out_scale, float eps) {
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= rows * heads) return;
+    const int r = w / heads, h = w % heads;
+    const float* a1 = y + (size_t)r * ldy + (size_t)h * dv;
+    const float* a2 = a1 + (size_t)heads * dv;
+    float q = 0.f;
+    for (int c = lane; c < dv; c += 32) {
+        const float d = fmaf(-lambda, a2[c], a1[c]);
+        q = fmaf(d, d, q);
+    }
+    q = warp_sum(q);
+    const float mul = out_scale / sqrtf(q / (float)dv + eps);
+    float* o = out + (size_t)r * ldo + (size_t)h * dv;
+    for (int c = lane; c < dv; c += 32) o[c] = fmaf(-lambda, a2[c], a1[c]) * mul;
+}
+
 template <typename TT>
 __global__ void embed_rows_kernel(const int32_t* __restrict__ tokens, const TT* __restrict__ table, float* __restrict__ x, int cols, int vocab,
-                                  int* err_flag) {
+                                  int* err_flag, float scale) {
     const size_t r = blockIdx.x;
     const int t = tokens[r];
     const bool ok = t >= 0 && t < vocab;
     if (!ok && threadIdx.x == 0 && err_flag != nullptr) err_flag[0] = 1;  // slot 0 = B2_ERR_TOKEN_RANGE
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) x[r * cols + c] = ok ? (float)table[(size_t)t * cols + c] : 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) x[r * cols + c] = ok ? (float)table[(size_t)t * cols + c] * scale : 0.f;
 }
 
 __global__ void sigmoid_gate_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ g, int64_t ldg, float* __restrict__ out,
@@ -431,11 +451,11 @@ int layernorm_gather_f32(const float* x, const int32_t* row_index, const float* 
 }
 
 int gated_group_rmsnorm_f32(const float* y, int64_t ldy, const float* z, int64_t ldz, const float* gamma, float* out, int64_t ldo, int rows,
-                            int cols, int group, int gate_first, float eps, cudaStream_t st) {
+                            int cols, int group, int gate_first, float eps, cudaStream_t st, int gamma_shared) {
     B2_CHECK_ARG(y && z && gamma && out && rows > 0 && group > 0 && cols % group == 0, "gated_group_rmsnorm: cols %d is not a multiple of the group %d",
                  cols, group);
     const int groups = cols / group, warps = rows * groups;
-    gated_group_rmsnorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(y, ldy, z, ldz, gamma, out, ldo, rows, groups, group, gate_first, 0, eps);
+    gated_group_rmsnorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(y, ldy, z, ldz, gamma, out, ldo, rows, groups, group, gate_first, gamma_shared, eps);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -449,13 +469,22 @@ int group_rmsnorm_f32(const float* y, int64_t ldy, const float* gamma, int gamma
     return 0;
 }
 
+int diff_combine_f32(const float* y, int64_t ldy, float* out, int64_t ldo, int rows, int heads, int dv, float lambda, float out_scale, float eps,
+                     cudaStream_t st) {
+    B2_CHECK_ARG(y && out && y != out && rows > 0 && heads > 0 && dv > 0, "diff_combine: bad argument");
+    const int warps = rows * heads;
+    diff_combine_kernel<<<(warps + 7) / 8, 256, 0, st>>>(y, ldy, out, ldo, rows, heads, dv, lambda, out_scale, eps);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
 int embed_rows_f32(const int32_t* tokens, const void* table, int table_dtype, float* x, int rows, int cols, int vocab, int* err_flag,
-                   cudaStream_t st) {
+                   cudaStream_t st, float scale) {
     B2_CHECK_ARG(tokens && table && x && rows > 0, "embed_rows: bad argument");
     if (table_dtype == DT_F32)
-        embed_rows_kernel<float><<<rows, 128, 0, st>>>(tokens, reinterpret_cast<const float*>(table), x, cols, vocab, err_flag);
+        embed_rows_kernel<float><<<rows, 128, 0, st>>>(tokens, reinterpret_cast<const float*>(table), x, cols, vocab, err_flag, scale);
     else
-        embed_rows_kernel<__nv_bfloat16><<<rows, 128, 0, st>>>(tokens, reinterpret_cast<const __nv_bfloat16*>(table), x, cols, vocab, err_flag);
+        embed_rows_kernel<__nv_bfloat16><<<rows, 128, 0, st>>>(tokens, reinterpret_cast<const __nv_bfloat16*>(table), x, cols, vocab, err_flag, scale);
     B2_LAUNCH_CHECK();
     return 0;
 }

@@ -205,6 +205,14 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
                     f = fmaf(1.f - low, 1.f / (1.f + expf(-(rd[u] + a.gate_bias[(size_t)h * dk + key]))), low);
                 }
                 sQ[e] = silu_f(rq[u]); sK[e] = 1.f - f; sD[e] = f;
+            } else if (MODE == SCAN_GLA) {
+                // decay per key channel: sigmoid(z + b)^(1 / tau) = exp(log_sigmoid(z + b) / tau), log_sigmoid(u) = min(u, 0) - log1p(exp(-|u|))
+                float al = 1.f;
+                if (key < dk) {
+                    const float z = rd[u] + a.gate_bias[(size_t)h * dk + key];
+                    al = expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) / a.tau);
+                }
+                sQ[e] = rq[u] * a.q_scale; sK[e] = rk[u]; sD[e] = al;
             } else {
                 sQ[e] = rq[u]; sK[e] = rk[u];
                 if (MODE == SCAN_RWKV) sD[e] = key < dk ? expf(-expf(rd[u])) : 1.f;
@@ -250,7 +258,7 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
                     if (MODE == SCAN_RWKV) {
                         acc = fmaf(q[i], fmaf(bon[i], kv, S[i]), acc);
                         S[i] = fmaf(d[i], S[i], kv);
-                    } else if (MODE == SCAN_HGRN2) {
+                    } else if (MODE == SCAN_HGRN2 || MODE == SCAN_GLA) {
                         S[i] = fmaf(d[i], S[i], kv);
                         acc = fmaf(q[i], S[i], acc);
                     } else {
@@ -357,6 +365,11 @@ int linear_scan_f32(const ScanArgs& a, cudaStream_t st) {
         B2_CHECK_ARG(a.gate_bias && a.gate_lower, "linear_scan(hgrn2): null gate bias / lower bound");
         return narrow ? launch_scan<SCAN_HGRN2, 8>(a, st) : launch_scan<SCAN_HGRN2, 16>(a, st);
     }
+    if (a.mode == SCAN_GLA) {
+        B2_CHECK_ARG(a.gate_bias && a.tau > 0.f, "linear_scan(gla): null decay bias or a non-positive tau");
+        return narrow ? launch_scan<SCAN_GLA, 8>(a, st) : launch_scan<SCAN_GLA, 16>(a, st);
+    }
+    B2_CHECK_ARG(a.mode == SCAN_RWKV, "linear_scan: unknown mode %d", a.mode);
     B2_CHECK_ARG(a.bonus != nullptr, "linear_scan(rwkv): null bonus");
     return narrow ? launch_scan<SCAN_RWKV, 8>(a, st) : launch_scan<SCAN_RWKV, 16>(a, st);
 }

@@ -1,10 +1,13 @@
-// Rotary positions for the layer-list decoders: pairs (2m, 2m+1) of a head's leading dimensions turn by position * f_m.
+// Rotary positions for the layer-list decoders: pairs (2m, 2m+1) of a head's leading dimensions (or, in the half layout, pairs
+// (m, m + pairs)) turn by position * f_m.
 // cos and sin come from a table [position][pair] that the cache builds on the host in double precision (the plain
 // frequencies base^(-2m/dims), optionally blended towards f_m / factor over a ramp of pairs with cos / sin scaled, the long-context
 // form known as YaRN), so an angle never carries the rounding of a 32-bit product of a large position. One kernel serves
 // queries (in place), keys and values on their way into the cache slabs, a rotated part copied to another layout, and the
-// turn back of an attention output by its query's position with the sigmoid output gate applied in the same pass. A second
-// kernel writes the row of a low-rank key/value cache that holds a normed latent AND one rotated key part.
+// turn back of an attention output by its query's position with the sigmoid output gate applied in the same pass. When a head is
+// normed before it turns (weighted RMS norm over the head, one weight vector for all heads), one warp takes a (row, head): it sums
+// the squares, then every lane norms and turns the pairs it owns. A further kernel writes the row of a low-rank key/value cache that
+// holds a normed latent AND one rotated key part.
 #include <math.h>
 
 #include <vector>
@@ -34,13 +37,13 @@ __device__ __forceinline__ void rotate_rows_body(const RotateArgs& a) {
                                     : a.out + (size_t)r * a.ld_out + (size_t)h * a.hs_out;
     const float* gate = a.gate != nullptr ? a.gate + (size_t)r * a.ldg + (size_t)h * a.size : nullptr;
     if (u >= a.offset && u < a.offset + a.pairs) {
-        const int mp = u - a.offset, d = a.offset + 2 * mp;
+        const int mp = u - a.offset, d = a.half ? a.offset + mp : a.offset + 2 * mp, d2 = a.half ? d + a.pairs : d + 1;
         const float2 cs = a.table[(size_t)pos * a.pairs + mp];
         const float sn = a.inverse ? -cs.y : cs.y;
-        const float x = src[d], y = src[d + 1];
+        const float x = src[d], y = src[d2];
         float o0 = x * cs.x - y * sn, o1 = y * cs.x + x * sn;
-        if (gate != nullptr) { o0 *= 1.f / (1.f + expf(-gate[d])); o1 *= 1.f / (1.f + expf(-gate[d + 1])); }
-        dst[d] = o0; dst[d + 1] = o1;
+        if (gate != nullptr) { o0 *= 1.f / (1.f + expf(-gate[d])); o1 *= 1.f / (1.f + expf(-gate[d2])); }
+        dst[d] = o0; dst[d2] = o1;
     } else {
         const int d = u < a.offset ? u : u + a.pairs;
         float o = src[d];
@@ -53,6 +56,52 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+// One warp per (row, head) of up to three parts: optional weighted RMS norm over the head, then the turn of its pairs. A lane reads
+// everything it writes before it writes (its own pairs and single entries), and the sum of squares is complete before any lane writes,
+// so the call may run in place.
+__global__ void __launch_bounds__(256) rotate_rows_warp_kernel(RotateParts ps, int n_parts) {
+    const int r = blockIdx.y, lane = threadIdx.x & 31;
+    int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int pi = 0;
+    while (pi < n_parts && w >= ps.p[pi].heads) { w -= ps.p[pi].heads; ++pi; }
+    if (pi >= n_parts) return;
+    const RotateArgs& a = ps.p[pi];
+    const int pos = a.row_pos[r];
+    if (pos < 0) return;
+    const int h = w;
+    const float* src = a.in + (size_t)r * a.ld_in + (size_t)h * a.hs_in;
+    float* dst = a.cache != nullptr ? a.cache + (((size_t)a.row_slot[r] * a.heads + h) * a.Smax + pos) * a.size
+                                    : a.out + (size_t)r * a.ld_out + (size_t)h * a.hs_out;
+    const float* gate = a.gate != nullptr ? a.gate + (size_t)r * a.ldg + (size_t)h * a.size : nullptr;
+    float mul = 1.f;
+    if (a.norm_w != nullptr) {
+        float q = 0.f;
+        for (int d = lane; d < a.size; d += 32) q = fmaf(src[d], src[d], q);
+        q = warp_sum(q);
+        mul = 1.f / sqrtf(q / (float)a.size + a.eps);
+    }
+    __syncwarp();
+    const int units = a.size - a.pairs;
+    for (int u = lane; u < units; u += 32) {
+        if (u >= a.offset && u < a.offset + a.pairs) {
+            const int mp = u - a.offset, d = a.half ? a.offset + mp : a.offset + 2 * mp, d2 = a.half ? d + a.pairs : d + 1;
+            const float2 cs = a.table[(size_t)pos * a.pairs + mp];
+            const float sn = a.inverse ? -cs.y : cs.y;
+            float x = src[d] * mul, y = src[d2] * mul;
+            if (a.norm_w != nullptr) { x *= a.norm_w[d]; y *= a.norm_w[d2]; }
+            float o0 = x * cs.x - y * sn, o1 = y * cs.x + x * sn;
+            if (gate != nullptr) { o0 *= 1.f / (1.f + expf(-gate[d])); o1 *= 1.f / (1.f + expf(-gate[d2])); }
+            dst[d] = o0; dst[d2] = o1;
+        } else {
+            const int d = u < a.offset ? u : u + a.pairs;
+            float o = src[d] * mul;
+            if (a.norm_w != nullptr) o *= a.norm_w[d];
+            if (gate != nullptr) o *= 1.f / (1.f + expf(-gate[d]));
+            dst[d] = o;
+        }
+    }
 }
 
 // cache[slot][pos] = [ unit_rms(in[r, :rank]) * gamma | the rot entries behind them, their first `pairs` pairs turned by pos ]
@@ -87,6 +136,7 @@ int rotate_rows_f32(const RotateArgs& a, cudaStream_t st) {
     B2_CHECK_ARG(a.in && (a.out || a.cache) && (a.table || a.pairs == 0) && a.row_pos && a.rows > 0 && a.heads > 0 && a.size > 0, "rotate_rows: bad argument");
     B2_CHECK_ARG(a.pairs >= 0 && a.offset >= 0 && a.offset + 2 * a.pairs <= a.size, "rotate_rows: %d pairs from %d do not fit a head of %d", a.pairs, a.offset, a.size);
     B2_CHECK_ARG(a.cache == nullptr || (a.row_slot != nullptr && a.Smax > 0), "rotate_rows: a cache destination needs slots");
+    if (a.norm_w != nullptr) return rotate_rows_multi_f32(&a, 1, st);
     const int units = a.heads * (a.size - a.pairs);
     rotate_rows_kernel<<<dim3((units + 255) / 256, a.rows), 256, 0, st>>>(a);
     B2_LAUNCH_CHECK();
@@ -96,7 +146,8 @@ int rotate_rows_f32(const RotateArgs& a, cudaStream_t st) {
 int rotate_rows_multi_f32(const RotateArgs* parts, int n, cudaStream_t st) {
     B2_CHECK_ARG(parts && n >= 1 && n <= 3, "rotate_rows_multi: 1..3 parts");
     RotateParts ps;
-    int units = 0;
+    int units = 0, heads = 0;
+    bool normed = false;
     for (int i = 0; i < n; ++i) {
         const RotateArgs& a = parts[i];
         B2_CHECK_ARG(a.in && (a.out || a.cache) && (a.table || a.pairs == 0) && a.row_pos && a.rows == parts[0].rows && a.heads > 0 && a.size > 0, "rotate_rows_multi: bad argument");
@@ -104,6 +155,13 @@ int rotate_rows_multi_f32(const RotateArgs* parts, int n, cudaStream_t st) {
         B2_CHECK_ARG(a.cache == nullptr || (a.row_slot != nullptr && a.Smax > 0), "rotate_rows_multi: a cache destination needs slots");
         ps.p[i] = a;
         units = std::max(units, a.heads * (a.size - a.pairs));
+        normed = normed || a.norm_w != nullptr;
+        heads += a.heads;
+    }
+    if (normed) {   // a normed head needs its sum of squares: one warp per (row, head) of every part
+        rotate_rows_warp_kernel<<<dim3((heads + 7) / 8, parts[0].rows), 256, 0, st>>>(ps, n);
+        B2_LAUNCH_CHECK();
+        return 0;
     }
     rotate_rows_multi_kernel<<<dim3((units + 255) / 256, parts[0].rows, n), 256, 0, st>>>(ps);
     B2_LAUNCH_CHECK();

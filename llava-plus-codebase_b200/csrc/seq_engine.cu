@@ -28,6 +28,9 @@ struct SeqWeights {   // tensors of one layer that owns its weights
     DevBuf canon1, canon2;                              // sandwich block: taps of the input convolutions [width][taps]
     DevBuf dq_norm, uq_w, ukx_w;                        // latent attention, further forms: norm of the queries' latent, W_uq, and W_uk widened per
                                                         // head by an identity block that carries the rotated key part ([H (dim + rot)][rank + rot])
+    DevBuf qn_w, kn_w, lam4;                            // grouped attention, further forms: weights of the q / k norm; [lq1 | lk1 | lq2 | lk2] of
+    float lambda = 0.f;                                 // differential attention and the layer's lambda (made from them when the model is finalized)
+    DevBuf gla_w, a2_w, a2_b, gnorm;                    // gated linear attention: [q | k | v | g | a1] fused, W_a2 and its bias, the heads' norm weight
     std::map<std::string, int> got;
 };
 
@@ -42,6 +45,7 @@ struct SeqLayerInfo {
     int pq = 0, pproj = 0, pproj_ld = 0;              // latent attention / HGRN2: width of q, of the fused projection, its pitch
     int pv = 0;                                       // heads * vdim of those mixers
     int lqw = 0, lqw_ld = 0, lrow = 0;                // latent attention: heads * (dim + rot_dim) and its pitch, a cache row (rank + rot_dim)
+    int maps = 1, gw = 0;                             // grouped attention: score maps per head (2: differential), width of the gate projection
 };
 struct SeqRun { int layer; int pass; int kv_run; };   // one layer run; pass >= 0: the run opens pass `pass` of the looped block; kv_run: the run
                                                       // whose cache rows a borrowing latent-attention layer reads (-1: its own)
@@ -75,7 +79,7 @@ struct SeqLayerState {
     DevBuf kc, vc, bucket_of;          // attention: [slots][G][Smax][dk], [slots][G][Smax][dv], int32 [Smax]
     DevBuf wkv, prev;                  // RWKV: [slots][heads][dim][dim], [slots][width]
     DevBuf lat;                        // latent attention: [slots][Smax][rank]
-    DevBuf gla;                        // HGRN2: [slots][heads][dim][vdim]
+    DevBuf gla;                        // HGRN2, gated linear attention: [slots][heads][dim][vdim]
     DevBuf canon1, canon2;             // sandwich block: the last taps-1 inputs of both sublayers [slots][taps-1][width]
     DevBuf rot_tab, vrot_tab;          // rotation tables (cos, sin) [Smax][pairs] of the queries / keys and of the values
 };
@@ -210,6 +214,7 @@ int attn_nsplit(int rows, int G, int max_seq) {
 static void mask_of(const b2_seq_layer_desc& d, BiasAttnArgs& aa) {
     aa.mask_kind = d.mask_kind;
     aa.mask_size = d.mask_size;
+    aa.mask_keep = d.mask_keep;
 }
 
 // Attention over a low-rank latent. S: the run's own state (rotation table); KS: the state whose cache rows it reads (its own,
@@ -263,7 +268,7 @@ static int latent_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeight
             B2_TRY(rotate_rows_f32(ra, st));
         }
         const float* lat = lat_cache + (size_t)slot * kv->max_seq * lrow;
-        const int first = d.mask_kind == B2_MASK_WINDOW ? std::max(0, ctx_end - R - d.mask_size + 1)
+        const int first = d.mask_kind == B2_MASK_WINDOW ? (d.mask_keep > 0 ? 0 : std::max(0, ctx_end - R - d.mask_size + 1))
                         : d.mask_kind == B2_MASK_CHUNK ? (ctx_end - R) / d.mask_size * d.mask_size : 0;
         const DevBuf& wk = rd > 0 ? W.ukx_w : W.uk_w;
         for (int m0 = first; m0 < ctx_end; m0 += s.rows) {
@@ -318,8 +323,10 @@ static int latent_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeight
     return lin(y, L.pv, W.o_w, width, L.pv, target, width, R, LIN_NONE, alpha, accumulate);
 }
 
-// Attention with grouped key/value heads, a short convolution on q / k / v, rotary q / k, optionally rotated values, a masked
-// softmax with an optional fixed sink, and a per-channel sigmoid output gate.
+// Attention with grouped key/value heads, a short convolution on q / k / v, an optional weighted norm of the q / k heads, rotary q / k in
+// either pair layout, optionally rotated values, a masked softmax with an optional fixed sink, and a sigmoid output gate per channel or
+// per head. With two maps (differential attention) the projection rows were ordered [map][head][dim] when the tensors were set, so the
+// maps are simply twice the query and key heads over the same value heads, and a head's two outputs are joined after the softmax.
 static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& W, SeqLayerState& S, const float* h, float* target, float alpha,
                      int accumulate, int R, int nseg, cudaStream_t st) {
     SeqModel& s = *m->seq;
@@ -327,12 +334,12 @@ static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& 
     const b2_seq_layer_desc& d = L.d;
     const Lin lin{m, st};
     const int width = s.d.width;
-    const int H = d.ga_heads, G = d.ga_kv_heads, dk = d.ga_dim, dv = d.ga_vdim;
+    const int H = d.ga_heads, G = d.ga_kv_heads, dk = d.ga_dim, dv = d.ga_vdim, maps = L.maps;
     const int max_n = nseg == 1 ? R : 1;
     const SeqSeg* segs = s.segs.as<SeqSeg>();
     const int32_t* row_slot = s.row_slot.as<int32_t>();
     const int32_t* row_pos = s.row_pos.as<int32_t>();
-    float* proj = s.proj.as<float>();  // [R, nq | nk | nv | ng]
+    float* proj = s.proj.as<float>();  // [R, nq | nk | nv | gate]
     B2_TRY(lin(h, width, W.lproj_w, L.lproj, width, proj, L.lproj_ld, R));
     float* qkv = proj;
     int64_t ldc = L.lproj_ld;
@@ -345,34 +352,80 @@ static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& 
     // says so): one launch
     RotateArgs rq[3];
     for (RotateArgs& ra : rq) { ra.rows = R; ra.row_slot = row_slot; ra.row_pos = row_pos; ra.Smax = kv->max_seq; ra.ld_in = ldc; ra.offset = 0; }
-    rq[0].in = qkv; rq[0].hs_in = dk; rq[0].out = qkv; rq[0].ld_out = ldc; rq[0].hs_out = dk; rq[0].heads = H; rq[0].size = dk;
-    rq[1].in = qkv + L.nq; rq[1].hs_in = dk; rq[1].cache = S.kc.as<float>(); rq[1].heads = G; rq[1].size = dk;
+    rq[0].in = qkv; rq[0].hs_in = dk; rq[0].out = qkv; rq[0].ld_out = ldc; rq[0].hs_out = dk; rq[0].heads = maps * H; rq[0].size = dk;
+    rq[1].in = qkv + L.nq; rq[1].hs_in = dk; rq[1].cache = S.kc.as<float>(); rq[1].heads = maps * G; rq[1].size = dk;
     rq[0].table = rq[1].table = S.rot_tab.as<float2>(); rq[0].pairs = rq[1].pairs = d.rot_dims / 2;
+    rq[0].half = rq[1].half = d.ga_rot_half;
+    if (d.ga_qk_norm) { rq[0].norm_w = W.qn_w.as<float>(); rq[1].norm_w = W.kn_w.as<float>(); rq[0].eps = rq[1].eps = s.d.norm_eps; }
     rq[2].in = qkv + L.nq + L.nk; rq[2].hs_in = dv; rq[2].cache = S.vc.as<float>(); rq[2].heads = G; rq[2].size = dv;
     rq[2].table = S.vrot_tab.as<float2>(); rq[2].pairs = d.ga_rot_values ? dv / 2 : 0;
     B2_TRY(rotate_rows_multi_f32(rq, 3, st));
     BiasAttnArgs aa;
     aa.q = qkv; aa.ldq = ldc;
     aa.kcache = S.kc.as<float>(); aa.vcache = S.vc.as<float>();
-    aa.out = s.y.as<float>(); aa.ldo = L.ng;
-    aa.H = H; aa.G = G; aa.dk = dk; aa.dv = dv; aa.Smax = kv->max_seq; aa.rows = R;
+    aa.out = s.y.as<float>(); aa.ldo = (int64_t)maps * L.ng;
+    aa.H = maps * H; aa.G = maps * G; aa.Gv = maps > 1 ? G : 0; aa.dk = dk; aa.dv = dv; aa.Smax = kv->max_seq; aa.rows = R;
     aa.scale = d.ga_scale;
     aa.sink_fixed = d.ga_sink != 0; aa.sink_value = d.ga_sink_value;
     aa.row_slot = row_slot; aa.row_pos = row_pos;
-    aa.nsplit = attn_nsplit(R, G, kv->max_seq);
+    aa.nsplit = attn_nsplit(R, maps * G, kv->max_seq);
     aa.tile_rows = max_n;
     if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
     aa.partial = state.attn_partial.as<float>();
     mask_of(d, aa);
     B2_TRY(attn_bias_f32(aa, st));
-    // every head's output is turned back by the query's position, and the sigmoid gate is applied in the same pass
-    RotateArgs rb;
-    rb.in = s.y.as<float>(); rb.ld_in = L.ng; rb.hs_in = dv; rb.out = s.gated.as<float>(); rb.ld_out = L.ng; rb.hs_out = dv;
-    rb.gate = proj + L.nq + L.nk + L.nv; rb.ldg = L.lproj_ld;
-    rb.table = S.vrot_tab.as<float2>(); rb.heads = H; rb.size = dv; rb.offset = 0; rb.pairs = d.ga_rot_values ? dv / 2 : 0; rb.inverse = 1;
-    rb.rows = R; rb.row_pos = row_pos;
-    B2_TRY(rotate_rows_f32(rb, st));
-    return lin(s.gated.as<float>(), L.ng, W.o_w, width, L.ng, target, width, R, LIN_NONE, alpha, accumulate);
+    const float* yo = s.y.as<float>();
+    float* gated = s.gated.as<float>();
+    const float* gates = proj + L.nq + L.nk + L.nv;
+    if (maps > 1) {   // a head's two maps: unit_rms(a1 - lambda a2) * (1 - diff)
+        B2_TRY(diff_combine_f32(yo, (int64_t)maps * L.ng, gated, L.ng, R, H, dv, W.lambda, 1.f - d.ga_diff, s.d.norm_eps, st));
+        yo = gated;
+    }
+    if (d.ga_rot_values || d.ga_gate == B2_GATE_CHANNEL) {
+        // every head's output is turned back by the query's position, and the per-channel sigmoid gate is applied in the same pass
+        RotateArgs rb;
+        rb.in = yo; rb.ld_in = L.ng; rb.hs_in = dv; rb.out = gated; rb.ld_out = L.ng; rb.hs_out = dv;
+        if (d.ga_gate == B2_GATE_CHANNEL) { rb.gate = gates; rb.ldg = L.lproj_ld; }
+        rb.table = S.vrot_tab.as<float2>(); rb.heads = H; rb.size = dv; rb.offset = 0; rb.pairs = d.ga_rot_values ? dv / 2 : 0; rb.inverse = 1;
+        rb.rows = R; rb.row_pos = row_pos;
+        B2_TRY(rotate_rows_f32(rb, st));
+        yo = gated;
+    }
+    if (d.ga_gate == B2_GATE_HEAD) {   // one sigmoid per head
+        B2_TRY(head_gate_f32(yo, L.ng, gates, L.lproj_ld, gated, L.ng, R, H, dv, st));
+        yo = gated;
+    }
+    return lin(yo, L.ng, W.o_w, width, L.ng, target, width, R, LIN_NONE, alpha, accumulate);
+}
+
+// Gated linear attention: one fused projection [q | k | v | g | a1], the decay logits through the second low-rank matrix, the
+// recurrence (decay, scaled query and state in fp32), per-head RMS norm with the gate, out-projection.
+static int gla_mixer(b2_model* m, const SeqLayerInfo& L, SeqWeights& W, SeqLayerState& S, const float* h, float* target, float alpha, int accumulate,
+                     int R, int nseg, cudaStream_t st) {
+    SeqModel& s = *m->seq;
+    const b2_seq_layer_desc& d = L.d;
+    const Lin lin{m, st};
+    const int width = s.d.width, H = d.gl_heads, dk = d.gl_dim, dv = d.gl_vdim;
+    float* proj = s.proj.as<float>();
+    B2_TRY(lin(h, width, W.gla_w, L.pproj, width, proj, L.pproj_ld, R));
+    float* z = s.wlog.as<float>();   // [R, heads * dim] decay logits without their bias (the recurrence adds it in fp32)
+    B2_TRY(lin(proj + 2 * L.pq + 2 * L.pv, L.pproj_ld, W.a2_w, L.pq, d.gl_rank, z, L.pq, R));
+    ScanArgs sa;
+    sa.mode = SCAN_GLA;
+    sa.q = proj; sa.ldq = L.pproj_ld;
+    sa.k = proj + L.pq; sa.ldk = L.pproj_ld;
+    sa.v = proj + 2 * L.pq; sa.ldv = L.pproj_ld;
+    sa.decay_in = z; sa.ldd = L.pq;
+    sa.gate_bias = W.a2_b.as<float>();
+    sa.q_scale = 1.f / sqrtf((float)dk); sa.tau = d.gl_tau;
+    sa.state = S.gla.as<float>();
+    sa.y = s.y.as<float>(); sa.ldy = L.pv;
+    sa.heads = H; sa.groups = H; sa.dk = dk; sa.dv = dv;
+    sa.segs = s.segs.as<SeqSeg>(); sa.nseg = nseg;
+    B2_TRY(linear_scan_f32(sa, st));
+    B2_TRY(gated_group_rmsnorm_f32(s.y.as<float>(), L.pv, proj + 2 * L.pq + L.pv, L.pproj_ld, W.gnorm.as<float>(), s.gated.as<float>(), L.pv, R, L.pv, dv,
+                                   0, s.d.norm_eps, st, 1));
+    return lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, target, width, R, LIN_NONE, alpha, accumulate);
 }
 
 // What a sublayer of a sandwich block reads: the pending sublayer output (weight `post`, in mixout) joins x, x is normed with
@@ -411,6 +464,23 @@ static int seq_feed_forward(b2_model* m, const SeqLayerInfo& L, SeqWeights& W, c
         B2_TRY(lin(h, width, W.up_w, d.ff, width, s.ff.as<float>(), ffl, R));
         B2_TRY(polynorm_f32(s.ff.as<float>(), ffl, W.up_b.as<float>(), W.act_coef.as<float>(), s.ffa.as<float>(), d.ff, R, d.ff, eps, st));
         return lin(s.ffa.as<float>(), d.ff, W.down_w, width, d.ff, target, width, R, LIN_NONE, alpha, accumulate, W.down_b.as<float>(), 0, W.down_b16.p);
+    }
+    if (d.ff_kind == B2_FF_CLAMP_GLU) {
+        // [gate | up] in one matrix; the bounded gated unit a(g) (u + 1); a decode step takes product and unit in one launch
+        const int ff = d.ff, ffl = (2 * ff + 7) / 8 * 8;
+        const GluAct act{d.ff_act_slope, d.ff_limit, 1.f};
+        if (R <= 8) {
+            GroupedLinearArgs gs;
+            gs.A = h; gs.lda = width; gs.a_div = 1; gs.W = W.up_w.p; gs.ldw = width; gs.w_group_stride = 0; gs.w_dtype = s.w_dtype;
+            gs.tile_group = s.zero_idx.as<int32_t>(); gs.tile_rows = 1; gs.out = s.ffa.as<float>(); gs.ld_out = ff;
+            gs.M = R; gs.N = ff; gs.K = width; gs.round_a = s.d.compute == B2_COMPUTE_BF16; gs.swiglu = 1;
+            gs.glu_slope = act.slope; gs.glu_limit = act.limit; gs.glu_up_shift = act.up_shift;
+            B2_TRY(linear_grouped_f32(gs, st));
+        } else {
+            B2_TRY(lin(h, width, W.up_w, 2 * ff, width, s.ff.as<float>(), ffl, R));
+            B2_TRY(glu_rows_f32(s.ff.as<float>(), ffl, s.ffa.as<float>(), ff, R, ff, act, st));
+        }
+        return lin(s.ffa.as<float>(), ff, W.down_w, width, ff, target, width, R, LIN_NONE, alpha, accumulate);
     }
     if (d.ff_kind != B2_FF_MOE) {
         B2_TRY(lin(h, width, W.up_w, d.ff, width, s.ff.as<float>(), (d.ff + 7) / 8 * 8, R, LIN_RELU_SQ));
@@ -515,7 +585,8 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
     float* mix = s.mixout.as<float>();
     const SeqSeg* segs = s.segs.as<SeqSeg>();
     const int max_n = nseg == 1 ? R : 1;  // a prompt portion is one segment of R rows; a decode step is R segments of one row
-    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1, sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS;
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1, sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS, parallel = s.d.block == B2_BLOCK_PARALLEL_RMS;
+    const bool direct = pre || parallel;   // a sublayer's last product adds residual_mult * its output onto x
     const float rm = s.d.residual_mult;
     float* xn = s.xn.as<float>();
     const float* post = nullptr;   // sandwich block: weight of the sublayer output in `mix` that has not joined x yet
@@ -529,20 +600,25 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
         const int pass = s.runs[ri].pass;
         const float* pass_add = pass > 0 ? s.x0.as<float>() : nullptr;
         const float* pass_vec = pass >= 0 ? s.loop_step.as<float>() + (size_t)pass * width : nullptr;
-        if (pre || sandwich) {
+        if (pre || sandwich || parallel) {
             // pre-norm block: a sublayer reads g * unit_rms(x) and adds residual_mult * its output onto x in its last product.
+            // parallel block: ONE weighted RMS norm per layer; mixer and feed-forward both read it and both add onto x the same way.
             // sandwich block: a sublayer reads u + conv(u), u = rms_w(x); its output lands in `mix`, and its weighted RMS norm joins x in
             // the same pass that norms x for the next sublayer (`post`: the weight of a sublayer output that has not joined x yet).
-            float* target = pre ? x : mix;
-            const float alpha = pre ? rm : 1.f;
+            float* target = direct ? x : mix;
+            const float alpha = direct ? rm : 1.f;
+            const int acc = direct ? 1 : 0;
             const float* h = xn;
             if (pre) B2_TRY(rms_scalar_f32(x, nullptr, W.norm1.as<float>(), pass_add, pass_vec, xn, R, width, eps, st));
+            else if (parallel) B2_TRY(rms_weight_f32(x, width, nullptr, W.norm1.as<float>(), xn, width, 0, R, width, eps, st));
             else B2_TRY(sandwich_input(s, post, W.norm1, W.canon1, S.canon1, R, nseg, max_n, st, &h));
             if (d.type == B2_MIXER_LATENT_ATTN) {
                 SeqLayerState& KS = d.la_kv_from > 0 ? state.layer[s.runs[ri].kv_run] : S;
-                B2_TRY(latent_mixer(m, kv, L, W, S, KS, h, target, alpha, pre ? 1 : 0, R, nseg, slot, ctx_end, st));
+                B2_TRY(latent_mixer(m, kv, L, W, S, KS, h, target, alpha, acc, R, nseg, slot, ctx_end, st));
             } else if (d.type == B2_MIXER_GQA_ATTN) {
-                B2_TRY(gqa_mixer(m, kv, L, W, S, h, target, alpha, pre ? 1 : 0, R, nseg, st));
+                B2_TRY(gqa_mixer(m, kv, L, W, S, h, target, alpha, acc, R, nseg, st));
+            } else if (d.type == B2_MIXER_GLA) {
+                B2_TRY(gla_mixer(m, L, W, S, h, target, alpha, acc, R, nseg, st));
             } else {
                 float* proj = s.proj.as<float>();  // [R, q | f | v]
                 const int H = d.g_heads, dk = d.g_dim, dv = d.g_vdim;
@@ -559,14 +635,14 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                 sa.segs = segs; sa.nseg = nseg;
                 B2_TRY(linear_scan_f32(sa, st));
                 B2_TRY(group_rmsnorm_f32(s.y.as<float>(), L.pv, W.hnorm.as<float>(), 1, s.gated.as<float>(), L.pv, R, L.pv, dv, eps, st));
-                B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, target, width, R, LIN_NONE, alpha, pre ? 1 : 0));
+                B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, target, width, R, LIN_NONE, alpha, acc));
             }
             post = sandwich ? W.norm1_b.as<float>() : nullptr;
             if (d.ff > 0) {
-                h = xn;
+                h = xn;   // parallel block: the feed-forward reads what the mixer read
                 if (pre) B2_TRY(rms_scalar_f32(x, nullptr, W.norm2.as<float>(), nullptr, nullptr, xn, R, width, eps, st));
-                else B2_TRY(sandwich_input(s, post, W.norm2, W.canon2, S.canon2, R, nseg, max_n, st, &h));
-                B2_TRY(seq_feed_forward(m, L, W, h, target, alpha, pre ? 1 : 0, R, st));
+                else if (sandwich) B2_TRY(sandwich_input(s, post, W.norm2, W.canon2, S.canon2, R, nseg, max_n, st, &h));
+                B2_TRY(seq_feed_forward(m, L, W, h, target, alpha, acc, R, st));
                 post = sandwich ? W.norm2_b.as<float>() : nullptr;
             }
             if (post != nullptr && (resid_out != nullptr || ri + 1 == s.runs.size())) {   // the last sublayer's output joins x now
@@ -671,7 +747,7 @@ static int seq_embed(b2_model* m, b2_kv* kv, const int32_t* tokens, int R, int n
         return embed_bigram_rows_f32(tokens, s.segs.as<SeqSeg>(), nseg, nseg == 1 ? R : 1, s.embed.p, s.bigram.p, s.w_dtype, kv->seq->last_tok.as<int32_t>(),
                                      s.x.as<float>(), s.x0.as<float>(), s.d.width, s.d.vocab, s.d.bigram_buckets, s.d.bigram_mul_prev, s.d.bigram_mul_cur,
                                      m->err_dev, st);
-    return embed_rows_f32(tokens, s.embed.p, s.w_dtype, s.x.as<float>(), R, s.d.width, s.d.vocab, m->err_dev, st);
+    return embed_rows_f32(tokens, s.embed.p, s.w_dtype, s.x.as<float>(), R, s.d.width, s.d.vocab, m->err_dev, st, s.d.embed_scale != 0.f ? s.d.embed_scale : 1.f);
 }
 
 // rows `index` (null: all) of x -> final norm -> head -> soft-cap: fp32 logits [n, vocab]
@@ -679,7 +755,7 @@ static int seq_head(b2_model* m, const int32_t* index, int n, float* logits, int
     SeqModel& s = *m->seq;
     if (s.d.block == B2_BLOCK_PRE_RMS1)
         B2_TRY(rms_scalar_f32(s.x.as<float>(), index, s.final_w.as<float>(), nullptr, nullptr, s.xn.as<float>(), n, s.d.width, s.d.norm_eps, st));
-    else if (s.d.block == B2_BLOCK_SANDWICH_RMS)
+    else if (s.d.block == B2_BLOCK_SANDWICH_RMS || s.d.block == B2_BLOCK_PARALLEL_RMS)
         B2_TRY(rms_weight_f32(s.x.as<float>(), s.d.width, index, s.final_w.as<float>(), s.xn.as<float>(), s.d.width, 0, n, s.d.width, s.d.norm_eps, st));
     else
         B2_TRY(layernorm_gather_f32(s.x.as<float>(), index, s.final_w.as<float>(), s.final_b.as<float>(), s.xn.as<float>(), n, s.d.width, s.d.norm_eps, st));
@@ -715,15 +791,15 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     const std::string k(key);
     if (k == "embed") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.embed, WD, (size_t)V * width, 0, ptr, dt, (int64_t)V * width); }
     if (k == "head") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.head, WD, (size_t)((V + 7) / 8 * 8) * width, 0, ptr, dt, (int64_t)V * width); }
-    const bool sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS;
-    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1 || sandwich;   // blocks whose layers are made of the mixers / feed-forwards below
-    if (k == "final.norm" && pre && !sandwich) { B2_TRY(want_shape(key, shape, ndim, 1)); s.got[k] = 1; return put_tensor(s.final_w, DT_F32, 1, 0, ptr, dt, 1); }
+    const bool sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS, parallel = s.d.block == B2_BLOCK_PARALLEL_RMS;
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1 || sandwich || parallel;   // blocks whose layers are made of the mixers / feed-forwards below
+    if (k == "final.norm" && s.d.block == B2_BLOCK_PRE_RMS1) { B2_TRY(want_shape(key, shape, ndim, 1)); s.got[k] = 1; return put_tensor(s.final_w, DT_F32, 1, 0, ptr, dt, 1); }
     if (k == "bigram" && s.d.bigram_buckets > 0) {
         const int64_t rows = (int64_t)s.d.bigram_buckets + 1;
         B2_TRY(want_shape(key, shape, ndim, rows, width)); s.got[k] = 1;
         return put_tensor(s.bigram, WD, (size_t)rows * width, 0, ptr, dt, rows * width);
     }
-    if (k == "loop.step" && s.d.loop_times >= 1) {
+    if (k == "loop.step" && s.d.loop_times >= 1 && !s.d.loop_plain) {
         B2_TRY(want_shape(key, shape, ndim, s.d.loop_times, width)); s.got[k] = 1;
         return put_tensor(s.loop_step, DT_F32, (size_t)s.d.loop_times * width, 0, ptr, dt, (int64_t)s.d.loop_times * width);
     }
@@ -764,6 +840,8 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
                 if (r == "norm2b") return vec(W.norm2_b, width);
                 if (r == "canon2" && ct >= 1) return taps_of(W.canon2, width, width, 0, ct);
             }
+        } else if (parallel) {
+            if (r == "norm1") return vec(W.norm1, width);
         } else {
             if (r == "norm1") return vec(W.norm1, 1);
             if (r == "norm2" && d.ff > 0) return vec(W.norm2, 1);
@@ -810,16 +888,59 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
                 return 0;
             }
         } else if (d.type == B2_MIXER_GQA_ATTN) {
-            // the four projections share their input: one [nq + nk + nv + ng, width] matrix, one product; the taps of q, k, v side by side
+            // the four projections share their input: one [nq + nk + nv + gate, width] matrix, one product; the taps of q, k, v side by side
             const char* parts[4] = {"mix.q", "mix.k", "mix.v", "mix.g"};
-            const int sizes[4] = {L.nq, L.nk, L.nv, L.ng};
+            const int sizes[4] = {L.nq, L.nk, L.nv, L.gw};
+            const int heads_of[2] = {d.ga_heads, d.ga_kv_heads};
             int row0 = 0;
             for (int j = 0; j < 4; ++j) {
-                if (r == parts[j]) return part(W.lproj_w, L.lproj, row0, sizes[j], width);
-                if (j < 3 && d.ga_conv >= 1 && r == std::string(parts[j]) + ".conv") return taps_of(W.conv_w, sizes[j], L.conv_ch, row0, d.ga_conv);
+                const bool is_w = r == parts[j] && sizes[j] > 0, is_taps = j < 3 && d.ga_conv >= 1 && r == std::string(parts[j]) + ".conv";
+                if ((is_w || is_taps) && j < 2 && L.maps > 1) {
+                    // two maps: the checkpoint orders the rows [head][map][dim]; here they lie [map][head][dim], so that the maps are further
+                    // heads (query head index = map * heads + head, the same for the keys) and share the value heads
+                    const int cols = is_w ? width : d.ga_conv, nh = heads_of[j], dk = d.ga_dim;
+                    B2_TRY(want_shape(key, shape, ndim, sizes[j], cols));
+                    W.got[r] = 1;
+                    const size_t sz = dt == DT_F32 ? 4 : 2;
+                    for (int hh = 0; hh < nh; ++hh)
+                        for (int mp = 0; mp < L.maps; ++mp) {
+                            const char* src = reinterpret_cast<const char*>(ptr) + (size_t)(hh * L.maps + mp) * dk * cols * sz;
+                            const size_t dst_row = (size_t)row0 + (size_t)(mp * nh + hh) * dk;
+                            if (is_w) B2_TRY(put_tensor(W.lproj_w, WD, (size_t)((L.lproj + 7) / 8 * 8) * cols, dst_row * cols, src, dt, (int64_t)dk * cols));
+                            else B2_TRY(put_tensor(W.conv_w, DT_F32, (size_t)L.conv_ch * cols, dst_row * cols, src, dt, (int64_t)dk * cols));
+                        }
+                    return 0;
+                }
+                if (is_w) return part(W.lproj_w, L.lproj, row0, sizes[j], width);
+                if (is_taps) return taps_of(W.conv_w, sizes[j], L.conv_ch, row0, d.ga_conv);
                 row0 += sizes[j];
             }
             if (r == "mix.o") return mat(W.o_w, width, L.ng);
+            if (d.ga_qk_norm) {
+                if (r == "mix.q.norm") return vec(W.qn_w, d.ga_dim);
+                if (r == "mix.k.norm") return vec(W.kn_w, d.ga_dim);
+            }
+            if (L.maps > 1) {
+                const char* lam[4] = {"mix.lq1", "mix.lk1", "mix.lq2", "mix.lk2"};
+                for (int j = 0; j < 4; ++j)
+                    if (r == lam[j]) {
+                        B2_TRY(want_shape(key, shape, ndim, d.ga_dim));
+                        W.got[r] = 1;
+                        return put_tensor(W.lam4, DT_F32, (size_t)4 * d.ga_dim, (size_t)j * d.ga_dim, ptr, dt, d.ga_dim);
+                    }
+            }
+        } else if (d.type == B2_MIXER_GLA) {
+            // [q | k | v | g | a1]: one matrix, one product
+            const int H = d.gl_heads, dk = d.gl_dim, dv = d.gl_vdim;
+            if (r == "mix.q") return part(W.gla_w, L.pproj, 0, L.pq, width);
+            if (r == "mix.k") return part(W.gla_w, L.pproj, L.pq, L.pq, width);
+            if (r == "mix.v") return part(W.gla_w, L.pproj, 2 * L.pq, L.pv, width);
+            if (r == "mix.g") return part(W.gla_w, L.pproj, 2 * L.pq + L.pv, L.pv, width);
+            if (r == "mix.a1") return part(W.gla_w, L.pproj, 2 * L.pq + 2 * L.pv, d.gl_rank, width);
+            if (r == "mix.a2") return mat(W.a2_w, (int64_t)H * dk, d.gl_rank);
+            if (r == "mix.a2.b") return vec(W.a2_b, (int64_t)H * dk);
+            if (r == "mix.norm") return vec(W.gnorm, dv);
+            if (r == "mix.o") return mat(W.o_w, width, (int64_t)H * dv);
         } else if (d.type == B2_MIXER_HGRN2) {
             const int H = d.g_heads, dk = d.g_dim, dv = d.g_vdim;
             if (r == "mix.q") return part(W.qfv_w, L.pproj, 0, L.pq, width);
@@ -869,6 +990,10 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
                     return put_tensor(W.ed_w, WD, ((size_t)E * width + 8) * ff, (size_t)e * width * ff, ptr, dt, (int64_t)width * ff);
                 }
             }
+        } else if (d.ff > 0 && d.ff_kind == B2_FF_CLAMP_GLU) {
+            if (r == "mlp.gate") return part(W.up_w, 2 * d.ff, 0, d.ff, width);
+            if (r == "mlp.up") return part(W.up_w, 2 * d.ff, d.ff, d.ff, width);
+            if (r == "mlp.down") return mat(W.down_w, width, d.ff);
         } else if (d.ff > 0) {
             if (r == "mlp.up") return mat(W.up_w, d.ff, width);
             if (r == "mlp.down") return mat(W.down_w, width, d.ff);
@@ -930,8 +1055,9 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     return -1;
 }
 
-static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre, bool sandwich, int ctaps) {
-    if (pre) {
+static std::vector<std::string> required_of(const SeqLayerInfo& L, int block, int ctaps) {
+    const bool sandwich = block == B2_BLOCK_SANDWICH_RMS, parallel = block == B2_BLOCK_PARALLEL_RMS;
+    if (block != B2_BLOCK_POST_LN) {
         std::vector<std::string> v = {"norm1", "mix.o"};
         const b2_seq_layer_desc& d = L.d;
         if (sandwich) { v.push_back("norm1b"); if (ctaps >= 1) v.push_back("canon1"); }
@@ -943,11 +1069,16 @@ static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre, boo
             if (!d.la_no_sink) v.push_back("mix.sink");
             if (!d.la_no_gate) v.push_back("mix.g");
         } else if (d.type == B2_MIXER_GQA_ATTN) {
-            for (const char* n : {"mix.q", "mix.k", "mix.v", "mix.g"}) v.push_back(n);
+            for (const char* n : {"mix.q", "mix.k", "mix.v"}) v.push_back(n);
+            if (L.gw > 0) v.push_back("mix.g");
             if (d.ga_conv >= 1) for (const char* n : {"mix.q.conv", "mix.k.conv", "mix.v.conv"}) v.push_back(n);
+            if (d.ga_qk_norm) for (const char* n : {"mix.q.norm", "mix.k.norm"}) v.push_back(n);
+            if (L.maps > 1) for (const char* n : {"mix.lq1", "mix.lk1", "mix.lq2", "mix.lk2"}) v.push_back(n);
+        } else if (d.type == B2_MIXER_GLA) {
+            for (const char* n : {"mix.q", "mix.k", "mix.v", "mix.g", "mix.a1", "mix.a2", "mix.a2.b", "mix.norm"}) v.push_back(n);
         } else for (const char* n : {"mix.q", "mix.f", "mix.f.b", "mix.lower", "mix.v", "mix.norm"}) v.push_back(n);
         if (L.d.ff > 0) {
-            v.push_back("norm2");
+            if (!parallel) v.push_back("norm2");
             if (sandwich) { v.push_back("norm2b"); if (ctaps >= 1) v.push_back("canon2"); }
             if (L.d.ff_kind == B2_FF_POLYNORM) for (const char* n : {"mlp.up", "mlp.up.b", "mlp.down", "mlp.down.b", "mlp.act"}) v.push_back(n);
             else if (L.d.ff_kind == B2_FF_MOE) {
@@ -959,7 +1090,8 @@ static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre, boo
                 if (L.d.moe_shared_ff > 0)
                     for (const char* n : {"mlp.shared.gate", "mlp.shared.up", "mlp.shared.down"})
                         if (gated || n[11] != 'g') v.push_back(n);
-            } else for (const char* n : {"mlp.up", "mlp.down"}) v.push_back(n);
+            } else if (L.d.ff_kind == B2_FF_CLAMP_GLU) for (const char* n : {"mlp.gate", "mlp.up", "mlp.down"}) v.push_back(n);
+            else for (const char* n : {"mlp.up", "mlp.down"}) v.push_back(n);
         }
         return v;
     }
@@ -980,32 +1112,46 @@ int seq_finalize(b2_model* m) {
     SeqModel& s = *m->seq;
     std::string missing;
     const bool sandwich = s.d.block == B2_BLOCK_SANDWICH_RMS;
-    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1 || sandwich;
+    const bool pre = s.d.block != B2_BLOCK_POST_LN;
     std::vector<std::string> top = {"embed", "head", "final.norm"};
     if (!pre) top.push_back("final.norm.b");
     if (s.d.bigram_buckets > 0) top.push_back("bigram");
-    if (s.d.loop_times >= 1) top.push_back("loop.step");
+    if (s.d.loop_times >= 1 && !s.d.loop_plain) top.push_back("loop.step");
     for (const std::string& n : top)
         if (!s.got.count(n) && missing.size() < 600) { missing += n; missing += ' '; }
     for (size_t i = 0; i < s.layers.size(); ++i) {
         if (s.layers[i].src != (int)i) continue;
-        for (const std::string& n : required_of(s.layers[i], pre, sandwich, s.d.input_conv_taps))
+        for (const std::string& n : required_of(s.layers[i], s.d.block, s.d.input_conv_taps))
             if (!s.w[i].got.count(n) && missing.size() < 600) missing += "l" + std::to_string(i) + "." + n + " ";
     }
     if (!missing.empty()) {
         set_error("b2_model_finalize: missing tensors: %s", missing.c_str());
         return -3;
     }
+    // differential attention: the layer's lambda from its four vectors (double precision on the host, once)
+    for (size_t i = 0; i < s.layers.size(); ++i) {
+        const SeqLayerInfo& L = s.layers[i];
+        if (L.src != (int)i || L.d.type != B2_MIXER_GQA_ATTN || L.maps < 2) continue;
+        const int dk = L.d.ga_dim;
+        std::vector<float> v((size_t)4 * dk);
+        B2_CUDA_CHECK(cudaMemcpy(v.data(), s.w[i].lam4.p, v.size() * F4, cudaMemcpyDeviceToHost));
+        double d1 = 0.0, d2 = 0.0;
+        for (int c = 0; c < dk; ++c) { d1 += (double)v[c] * v[dk + c]; d2 += (double)v[2 * dk + c] * v[3 * dk + c]; }
+        s.w[i].lambda = (float)(exp(d1) - exp(d2) + (double)L.d.ga_diff);
+    }
     const int width = s.d.width;
     int pw = 1, aw = 1, yw = 1, rw = 1, kw = 1, fw = 1;
     int latw = 0, moe_top = 0, moe_e = 0, moe_ff = 0;
+    bool glu = false;
     for (const SeqLayerInfo& L : s.layers) {
         if (L.d.type == B2_MIXER_MAMBA2) {
             pw = std::max(pw, L.dproj_ld); aw = std::max(aw, L.conv_ch); yw = std::max(yw, L.inner);
         } else if (L.d.type == B2_MIXER_PARALLEL) {
             pw = std::max(pw, L.lproj_ld); yw = std::max(yw, std::max(L.ng, L.rn)); rw = std::max(rw, L.rn); kw = std::max(kw, L.d.r_decay_rank);
         } else if (L.d.type == B2_MIXER_GQA_ATTN) {
-            pw = std::max(pw, L.lproj_ld); yw = std::max(yw, L.ng); aw = std::max(aw, L.conv_ch);
+            pw = std::max(pw, L.lproj_ld); yw = std::max(yw, L.maps * L.ng); aw = std::max(aw, L.conv_ch);
+        } else if (L.d.type == B2_MIXER_GLA) {
+            pw = std::max(pw, L.pproj_ld); yw = std::max(yw, L.pv); rw = std::max(rw, L.pq);
         } else {
             pw = std::max(pw, L.pproj_ld); yw = std::max(yw, L.pv);
             if (L.d.type == B2_MIXER_LATENT_ATTN) {
@@ -1014,6 +1160,7 @@ int seq_finalize(b2_model* m) {
             }
         }
         fw = std::max(fw, (L.d.ff + 7) / 8 * 8);
+        if (L.d.ff > 0 && L.d.ff_kind == B2_FF_CLAMP_GLU) { fw = std::max(fw, (2 * L.d.ff + 7) / 8 * 8); glu = true; }
         if (L.d.ff > 0 && L.d.ff_kind == B2_FF_MOE) {
             fw = std::max(fw, (2 * L.d.moe_shared_ff + 7) / 8 * 8);
             moe_top = std::max(moe_top, L.d.moe_top); moe_e = std::max(moe_e, L.d.moe_experts); moe_ff = std::max(moe_ff, L.d.ff);
@@ -1036,7 +1183,11 @@ int seq_finalize(b2_model* m) {
     B2_TRY(s.xn.alloc(R * width * F4));
     if (pre) B2_TRY(s.ffa.alloc(R * fw * F4));
     if (sandwich && s.d.input_conv_taps >= 1) B2_TRY(s.hin.alloc(R * width * F4));
-    if (s.d.loop_times > 1) B2_TRY(s.x0.alloc(R * width * F4));
+    if (s.d.loop_times > 1 && !s.d.loop_plain) B2_TRY(s.x0.alloc(R * width * F4));
+    if (glu && moe_e == 0) {   // the one-row grouped product of a decode step reads its group (always 0) from here
+        B2_TRY(s.zero_idx.alloc(64 * 4));
+        B2_CUDA_CHECK(cudaMemset(s.zero_idx.p, 0, 64 * 4));
+    }
     if (latw > 0) {
         s.lat_w = latw;
         B2_TRY(s.qabs.alloc(R * latw * F4));
@@ -1085,7 +1236,8 @@ void seq_model_free(b2_model* m) {
         DevBuf* bs[] = {&W.norm1, &W.norm1_b, &W.norm2, &W.norm2_b, &W.in_w, &W.conv_w, &W.conv_b, &W.dt_bias, &W.a_log, &W.skip, &W.mnorm, &W.o_w,
                         &W.lproj_w, &W.rel, &W.lo_w, &W.mu, &W.r_w, &W.k_w, &W.v_w, &W.g_w, &W.w1, &W.w2, &W.w0, &W.bonus, &W.rnorm, &W.ro_w,
                         &W.up_w, &W.down_w, &W.qdg_w, &W.dkv_norm, &W.uk_w, &W.ukT, &W.uv_w, &W.sink, &W.qfv_w, &W.f_b, &W.lower, &W.hnorm, &W.up_b, &W.down_b,
-                        &W.down_b16, &W.act_coef, &W.router_w, &W.egu_w, &W.ed_w, &W.sgu_w, &W.sd_w, &W.canon1, &W.canon2, &W.dq_norm, &W.uq_w, &W.ukx_w};
+                        &W.down_b16, &W.act_coef, &W.router_w, &W.egu_w, &W.ed_w, &W.sgu_w, &W.sd_w, &W.canon1, &W.canon2, &W.dq_norm, &W.uq_w, &W.ukx_w,
+                        &W.qn_w, &W.kn_w, &W.lam4, &W.gla_w, &W.a2_w, &W.a2_b, &W.gnorm};
         for (DevBuf* b : bs) b->free();
     }
     DevBuf* bs[] = {&s.embed, &s.head, &s.final_w, &s.final_b, &s.x, &s.proj, &s.act, &s.y, &s.gated, &s.mixout, &s.mixes, &s.rp, &s.wl1, &s.wlog,
@@ -1116,7 +1268,8 @@ int64_t seq_kv_bytes(const b2_model* m, int B, int Smax) {
         else if (d.type == B2_MIXER_PARALLEL)
             n += (int64_t)B * d.a_kv_heads * Smax * (d.a_dim + d.a_vdim) + (int64_t)B * d.r_heads * d.r_dim * d.r_dim + (int64_t)B * m->seq->d.width;
         else if (d.type == B2_MIXER_LATENT_ATTN) n += d.la_kv_from == 0 ? (int64_t)B * Smax * L.lrow : 0;
-        else if (d.type == B2_MIXER_GQA_ATTN) n += (int64_t)B * d.ga_kv_heads * Smax * (d.ga_dim + d.ga_vdim) + (int64_t)B * std::max(0, d.ga_conv - 1) * L.conv_ch;
+        else if (d.type == B2_MIXER_GQA_ATTN) n += (int64_t)B * d.ga_kv_heads * Smax * (L.maps * d.ga_dim + d.ga_vdim) + (int64_t)B * std::max(0, d.ga_conv - 1) * L.conv_ch;
+        else if (d.type == B2_MIXER_GLA) n += (int64_t)B * d.gl_heads * d.gl_dim * d.gl_vdim;
         else n += (int64_t)B * d.g_heads * d.g_dim * d.g_vdim;
         if (m->seq->d.block == B2_BLOCK_SANDWICH_RMS && m->seq->d.input_conv_taps > 1)
             n += (int64_t)B * (m->seq->d.input_conv_taps - 1) * m->seq->d.width * (d.ff > 0 ? 2 : 1);
@@ -1154,7 +1307,7 @@ int seq_kv_alloc(b2_kv* kv) {
             B2_TRY(rotary_table_build(rdesc, (int)Smax, S.rot_tab.as<float2>()));
         }
         if (d.type == B2_MIXER_GQA_ATTN) {
-            B2_TRY(S.kc.alloc(B * d.ga_kv_heads * Smax * d.ga_dim * F4));
+            B2_TRY(S.kc.alloc(B * L.maps * d.ga_kv_heads * Smax * d.ga_dim * F4));
             B2_TRY(S.vc.alloc(B * d.ga_kv_heads * Smax * d.ga_vdim * F4));
             cudaMemset(S.kc.p, 0, S.kc.bytes);
             cudaMemset(S.vc.p, 0, S.vc.bytes);
@@ -1168,7 +1321,7 @@ int seq_kv_alloc(b2_kv* kv) {
                 B2_TRY(S.vrot_tab.alloc(Smax * (d.ga_vdim / 2) * sizeof(float2)));
                 B2_TRY(rotary_table_build(vdesc, (int)Smax, S.vrot_tab.as<float2>()));
             }
-            maxH = std::max(maxH, d.ga_heads);
+            maxH = std::max(maxH, L.maps * d.ga_heads);
             maxdv = std::max(maxdv, d.ga_vdim);
         } else if (d.type == B2_MIXER_LATENT_ATTN) {
             if (d.la_kv_from == 0) {   // a borrowing layer reads the owner's rows
@@ -1179,6 +1332,9 @@ int seq_kv_alloc(b2_kv* kv) {
             maxdv = std::max(maxdv, d.la_rank);
         } else if (d.type == B2_MIXER_HGRN2) {
             B2_TRY(S.gla.alloc(B * d.g_heads * d.g_dim * d.g_vdim * F4));
+            cudaMemset(S.gla.p, 0, S.gla.bytes);
+        } else if (d.type == B2_MIXER_GLA) {
+            B2_TRY(S.gla.alloc(B * d.gl_heads * d.gl_dim * d.gl_vdim * F4));
             cudaMemset(S.gla.p, 0, S.gla.bytes);
         } else if (d.type == B2_MIXER_MAMBA2) {
             B2_TRY(S.ssm.alloc(B * d.m_heads * d.m_state * d.m_vdim * F4));
@@ -1245,7 +1401,8 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
     B2_CHECK_ARG(d.compute == B2_COMPUTE_BF16 || d.compute == B2_COMPUTE_F32, "b2_seq_model_create: unknown compute mode %d", d.compute);
     B2_CHECK_ARG(d.max_batch >= 1 && d.max_rows >= 1, "b2_seq_model_create: bad workspace sizing");
     B2_CHECK_ARG(d.norm_eps >= 0.f, "b2_seq_model_create: negative eps");
-    B2_CHECK_ARG(d.block == B2_BLOCK_POST_LN || d.block == B2_BLOCK_PRE_RMS1 || d.block == B2_BLOCK_SANDWICH_RMS, "b2_seq_model_create: unknown block form %d", d.block);
+    B2_CHECK_ARG(d.block >= B2_BLOCK_POST_LN && d.block <= B2_BLOCK_PARALLEL_RMS, "b2_seq_model_create: unknown block form %d", d.block);
+    B2_CHECK_ARG(d.embed_scale == 0.f || d.bigram_buckets == 0, "b2_seq_model_create: a scaled embedding does not go with the hashed bigram rows");
     B2_CHECK_ARG(d.input_conv_taps >= 0 && d.input_conv_taps <= 16, "b2_seq_model_create: 0..16 taps of the input convolution");
     B2_CHECK_ARG(d.input_conv_taps == 0 || d.block == B2_BLOCK_SANDWICH_RMS, "b2_seq_model_create: the input convolution belongs to the sandwich block");
     B2_CHECK_ARG(d.bigram_buckets >= 0 && d.logit_softcap >= 0.f, "b2_seq_model_create: negative bigram buckets or soft-cap");
@@ -1326,8 +1483,15 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             else if (l.rot_factor > 0.f && !(l.rot_original > 0.f && l.rot_fast > 0.f && l.rot_slow > 0.f && l.rot_base > 1.f)) why = "rotation: scaled frequencies need original, fast and slow";
             else if (l.ga_rot_values && !(l.rot_base > 0.f)) why = "attention: rotated values need a base";
             else if (l.mask_kind < B2_MASK_CAUSAL || l.mask_kind > B2_MASK_CHUNK || (l.mask_kind != B2_MASK_CAUSAL && l.mask_size < 1)) why = "mask: unknown kind or empty size";
-            L.nq = l.ga_heads * l.ga_dim; L.nk = l.ga_kv_heads * l.ga_dim; L.nv = l.ga_kv_heads * l.ga_vdim; L.ng = l.ga_heads * l.ga_vdim;
-            L.lproj = L.nq + L.nk + L.nv + L.ng;
+            else if (l.mask_keep < 0 || (l.mask_keep > 0 && l.mask_kind != B2_MASK_WINDOW)) why = "mask: kept first positions belong to a window";
+            else if (l.ga_maps < 0 || l.ga_maps > 2) why = "attention: one or two maps";
+            else if (l.ga_maps == 2 && l.ga_rot_values) why = "attention: two maps do not go with rotated values";
+            else if (l.ga_gate < B2_GATE_CHANNEL || l.ga_gate > B2_GATE_NONE) why = "attention: unknown output gate";
+            else if (l.ga_rot_half && l.rot_dims % 2) why = "attention: the half layout rotates an even number of dimensions";
+            L.maps = l.ga_maps == 2 ? 2 : 1;
+            L.nq = L.maps * l.ga_heads * l.ga_dim; L.nk = L.maps * l.ga_kv_heads * l.ga_dim; L.nv = l.ga_kv_heads * l.ga_vdim; L.ng = l.ga_heads * l.ga_vdim;
+            L.gw = l.ga_gate == B2_GATE_CHANNEL ? L.ng : l.ga_gate == B2_GATE_HEAD ? l.ga_heads : 0;
+            L.lproj = L.nq + L.nk + L.nv + L.gw;
             L.lproj_ld = (L.lproj + 7) / 8 * 8;
             L.conv_ch = L.nq + L.nk + L.nv;
         } else if (l.type == B2_MIXER_HGRN2) {
@@ -1335,11 +1499,17 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             L.pq = l.g_heads * l.g_dim; L.pv = l.g_heads * l.g_vdim;
             L.pproj = 2 * L.pq + L.pv;
             L.pproj_ld = (L.pproj + 7) / 8 * 8;
+        } else if (l.type == B2_MIXER_GLA) {
+            if (l.gl_heads < 1 || l.gl_dim < 1 || l.gl_dim > 256 || l.gl_vdim < 1 || l.gl_rank < 1) why = "gla: heads, dim 1..256, vdim, decay rank";
+            else if (!(l.gl_tau > 0.f)) why = "gla: tau must be positive";
+            L.pq = l.gl_heads * l.gl_dim; L.pv = l.gl_heads * l.gl_vdim;
+            L.pproj = 2 * L.pq + 2 * L.pv + l.gl_rank;
+            L.pproj_ld = (L.pproj + 7) / 8 * 8;
         } else {
             why = "unknown mixer type";
         }
-        const bool pre_mixer = l.type == B2_MIXER_LATENT_ATTN || l.type == B2_MIXER_HGRN2 || l.type == B2_MIXER_GQA_ATTN;
-        if (why == nullptr && pre_mixer != (d.block == B2_BLOCK_PRE_RMS1 || d.block == B2_BLOCK_SANDWICH_RMS)) why = "this mixer does not go with the model's block form";
+        const bool pre_mixer = l.type == B2_MIXER_LATENT_ATTN || l.type == B2_MIXER_HGRN2 || l.type == B2_MIXER_GQA_ATTN || l.type == B2_MIXER_GLA;
+        if (why == nullptr && pre_mixer != (d.block != B2_BLOCK_POST_LN)) why = "this mixer does not go with the model's block form";
         if (why == nullptr && l.ff > 0) {
             if (l.ff_kind != B2_FF_RELU_SQ && d.block == B2_BLOCK_POST_LN) why = "this feed-forward needs a pre-norm or sandwich block";
             else if (l.ff_kind == B2_FF_MOE) {
@@ -1347,6 +1517,8 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
                 else if (l.moe_groups < 1 || l.moe_experts % l.moe_groups || l.moe_keep < 1 || l.moe_keep > l.moe_groups) why = "moe: groups must divide experts, 1 <= keep <= groups";
                 else if (l.moe_shared_ff < 0) why = "moe: negative shared width";
                 else if (l.moe_score < 0 || l.moe_score > 1 || l.moe_group_score < 0 || l.moe_group_score > 1 || l.moe_act < 0 || l.moe_act > 1) why = "moe: unknown score, group score or activation";
+            } else if (l.ff_kind == B2_FF_CLAMP_GLU) {
+                if (l.ff_limit < 0.f) why = "gated feed-forward: negative limit";
             } else if (l.ff_kind != B2_FF_RELU_SQ && l.ff_kind != B2_FF_POLYNORM) why = "unknown feed-forward kind";
         }
         if (why == nullptr && L.src != i) {
@@ -1371,7 +1543,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
         for (int i = 0; i < d.n_layers; ++i) {
             if (looped && i == d.loop_start) {
                 for (int t = 0; t < d.loop_times; ++t)
-                    for (int j = d.loop_start; j < d.loop_stop; ++j) s->runs.push_back(SeqRun{j, j == d.loop_start ? t : -1, -1});
+                    for (int j = d.loop_start; j < d.loop_stop; ++j) s->runs.push_back(SeqRun{j, (j == d.loop_start && !d.loop_plain) ? t : -1, -1});
                 i = d.loop_stop - 1;
             } else {
                 s->runs.push_back(SeqRun{i, -1, -1});

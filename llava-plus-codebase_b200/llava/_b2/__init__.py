@@ -74,7 +74,11 @@ class SeqLayerDesc(_c.Structure):
                 ("ga_rot_values", _c.c_int32), ("ga_sink", _c.c_int32), ("ga_scale", _c.c_float), ("ga_sink_value", _c.c_float),
                 ("mask_kind", _c.c_int32), ("mask_size", _c.c_int32), ("rot_dims", _c.c_int32),
                 ("rot_base", _c.c_float), ("rot_factor", _c.c_float), ("rot_original", _c.c_float), ("rot_fast", _c.c_float),
-                ("rot_slow", _c.c_float)]
+                ("rot_slow", _c.c_float),
+                ("ga_maps", _c.c_int32), ("ga_diff", _c.c_float), ("ga_qk_norm", _c.c_int32), ("ga_rot_half", _c.c_int32),
+                ("ga_gate", _c.c_int32), ("mask_keep", _c.c_int32),
+                ("gl_heads", _c.c_int32), ("gl_dim", _c.c_int32), ("gl_vdim", _c.c_int32), ("gl_rank", _c.c_int32), ("gl_tau", _c.c_float),
+                ("ff_limit", _c.c_float), ("ff_act_slope", _c.c_float)]
 
 
 class SeqModelDesc(_c.Structure):
@@ -84,12 +88,13 @@ class SeqModelDesc(_c.Structure):
                 ("block", _c.c_int32), ("residual_mult", _c.c_float), ("logit_softcap", _c.c_float),
                 ("bigram_buckets", _c.c_int32), ("bigram_mul_prev", _c.c_int32), ("bigram_mul_cur", _c.c_int32),
                 ("loop_start", _c.c_int32), ("loop_stop", _c.c_int32), ("loop_times", _c.c_int32),
-                ("logit_scale", _c.c_float), ("input_conv_taps", _c.c_int32)]
+                ("logit_scale", _c.c_float), ("input_conv_taps", _c.c_int32), ("embed_scale", _c.c_float), ("loop_plain", _c.c_int32)]
 
 
-MIXER_MAMBA2, MIXER_PARALLEL, MIXER_LATENT_ATTN, MIXER_HGRN2, MIXER_GQA_ATTN = 1, 2, 3, 4, 5
-FF_RELU_SQ, FF_POLYNORM, FF_MOE = 0, 1, 2
-BLOCK_POST_LN, BLOCK_PRE_RMS1, BLOCK_SANDWICH_RMS = 0, 1, 2
+MIXER_MAMBA2, MIXER_PARALLEL, MIXER_LATENT_ATTN, MIXER_HGRN2, MIXER_GQA_ATTN, MIXER_GLA = 1, 2, 3, 4, 5, 6
+FF_RELU_SQ, FF_POLYNORM, FF_MOE, FF_CLAMP_GLU = 0, 1, 2, 3
+BLOCK_POST_LN, BLOCK_PRE_RMS1, BLOCK_SANDWICH_RMS, BLOCK_PARALLEL_RMS = 0, 1, 2, 3
+GATE_CHANNEL, GATE_HEAD, GATE_NONE = 0, 1, 2
 MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
 MOE_SCORE_SIGMOID, MOE_SCORE_SOFTMAX = 0, 1
 MOE_GROUP_TOP2_SUM, MOE_GROUP_MAX = 0, 1

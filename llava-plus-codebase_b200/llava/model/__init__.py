@@ -12,14 +12,16 @@ MODEL_REGISTRY = {
     "Katadra": ("language_model.katadra", "KatadraForCausalLM"),
     "Pefivik": ("language_model.pefivik", "PefivikForCausalLM"),
     "Fezuzen": ("language_model.fezuzen", "FezuzenForCausalLM"),
+    "Sofopel": ("language_model.sofopel", "SofopelForCausalLM"),
 }
 _LAZY = {"LlavaLlamaForCausalLM": "language_model.llava_llama", "LlavaConfig": "language_model.llava_llama",
          "KatadraForCausalLM": "language_model.katadra", "KatadraConfig": "language_model.katadra",
          "PefivikForCausalLM": "language_model.pefivik", "PefivikConfig": "language_model.pefivik",
-         "FezuzenForCausalLM": "language_model.fezuzen", "FezuzenConfig": "language_model.fezuzen"}
+         "FezuzenForCausalLM": "language_model.fezuzen", "FezuzenConfig": "language_model.fezuzen",
+         "SofopelForCausalLM": "language_model.sofopel", "SofopelConfig": "language_model.sofopel"}
 
 __all__ = ["LlavaConfig", "LlavaLlamaForCausalLM", "KatadraConfig", "KatadraForCausalLM", "PefivikConfig", "PefivikForCausalLM", "FezuzenConfig",
-           "FezuzenForCausalLM", "MODEL_REGISTRY",
+           "FezuzenForCausalLM", "SofopelConfig", "SofopelForCausalLM", "MODEL_REGISTRY",
            "model_class_for"]
 
 
