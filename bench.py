@@ -55,11 +55,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the side measurements of the other BASELINE configs")
-    ap.add_argument("--arch", default="llava", choices=["llava", "katadra", "pefivik", "fezuzen"],
+    ap.add_argument("--arch", default="llava", choices=["llava", "katadra", "pefivik", "fezuzen", "sofopel"],
                     help="katadra: prefill / decode throughput of the layer-list decoder beside the LLaMA decoder of equal width, "
                          "depth and parameter count (random weights); the default workload and its JSON line are unchanged")
-    ap.add_argument("--widths", default="2048,4096", help="--arch katadra / pefivik / fezuzen: model widths to measure")
-    ap.add_argument("--ctx", type=int, default=2048, help="--arch katadra / pefivik / fezuzen: prompt length")
+    ap.add_argument("--widths", default="2048,4096", help="--arch katadra / pefivik / fezuzen / sofopel: model widths to measure")
+    ap.add_argument("--ctx", type=int, default=2048, help="--arch katadra / pefivik / fezuzen / sofopel: prompt length")
     return ap.parse_args()
 
 
@@ -952,6 +952,79 @@ def run_fezuzen(args):
     print(json.dumps(out))
 
 
+def sofopel_config(width, ctx):
+    """Four parallel-block layers of the sizes a model of this width would have: window attention (heads of 128, four query heads per
+    key/value head, q / k norm, half-layout rotation with scaled frequencies, a window of half the prompt that keeps the first 4
+    positions, head gates), differential attention (two maps of 64 per head over values of 128, 4-tap convolutions, chunks of half the
+    prompt), gated linear attention (keys of 128, values of 256, a decay projection of rank 16) and window attention again, each beside a
+    bounded gated feed-forward of 2.5 x width."""
+    heads = width // 128
+    rot = {"base": 10000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    win = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "mask": {"size": ctx // 2, "keep_first": 4},
+                                            "rot": rot, "scale": 128 ** -0.5}}
+    dif = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "conv": 4, "diff": 0.8, "mask": {"size": ctx // 2},
+                                          "rot": {"base": 1.0e6, "dims": 64}, "scale": 64 ** -0.5}}
+    gla = {"type": "gla", "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "tau": 16.0}}
+    mlp = {"kind": "dense", "ff": 5 * width // 2, "limit": 7.0}
+    return {"architecture": "Sofopel", "width": width, "vocab": 32000, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "residual_mult": 0.5,
+            "layers": [dict(win, mlp=mlp), dict(dif, mlp=mlp), dict(gla, mlp=mlp), dict(win, mlp=mlp)]}
+
+
+def sofopel_params(cfg, rank=16):
+    """(matmul parameters a token multiplies with, function B -> parameters a decode step of B slots reads)"""
+    W = cfg["width"]
+    n = cfg["vocab"] * W
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        H = m["heads"]
+        if layer["type"] == "gla":
+            n += (2 * H * m["dim"] + 2 * H * m["vdim"] + rank) * W + H * m["dim"] * rank + W * H * m["vdim"]
+        else:
+            G, maps = m["kv_heads"], 2 if layer["type"] == "attention" else 1
+            n += (maps * (H + G) * m["dim"] + G * m["vdim"] + (H if maps == 1 else 0)) * W + W * H * m["vdim"]
+        if layer.get("mlp"):
+            n += 3 * layer["mlp"]["ff"] * W
+    return n, lambda B: n
+
+
+def run_sofopel(args):
+    """Sofopel beside Fezuzen, the package's closest model (the same grouped-attention mixer, convolutions, masks and Linears), at equal
+    width and depth."""
+    from oracle import fezuzen_oracle as FO
+    from oracle import sofopel_oracle as SO
+    from llava.model import FezuzenConfig, FezuzenForCausalLM, SofopelConfig, SofopelForCausalLM
+    from llava._b2 import launch_count
+
+    dev = torch.device("cuda:0")
+    hbm, tfl, src = peaks()
+    pk = {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}
+    S, N, layers = args.ctx, 64, 4
+    flush = torch.zeros(160 * 1024 * 1024 // 4, device=dev)  # 160 MB > 126 MB of L2
+    out = {"metric": "Sofopel vs Fezuzen (layer-list decoders) at equal width and depth", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+           "peaks": pk, "prompt": S, "decode_steps": N, "l2": "160 MB written before every timed run", "sizes": []}
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    for width in [int(w) for w in args.widths.split(",")]:
+        row = {"width": width, "layers": layers}
+        for name, mk_cfg, mk_params, mk_w, cfg_cls, model_cls in (
+                ("sofopel", lambda: sofopel_config(width, S), sofopel_params, lambda c: SO.random_weights(c, seed=0, ranks={2: 16}), SofopelConfig, SofopelForCausalLM),
+                ("fezuzen", lambda: fezuzen_config(width, S), fezuzen_params, lambda c: FO.random_weights(c, seed=0), FezuzenConfig, FezuzenForCausalLM)):
+            cfg = mk_cfg()
+            w = mk_w(cfg)
+            params, params_read = mk_params(cfg)
+            model = model_cls(cfg_cls(**cfg), {k: torch.from_numpy(np.asarray(v, np.float32)).bfloat16() for k, v in w.items()}, device=dev, dtype=torch.bfloat16,
+                              max_batch=8, max_seq=S + N + 8, max_rows=S)
+            row[name + "_params_total"] = int(sum(v.size for k, v in w.items() if v.ndim == 2 and k != "embed"))
+            del w
+            row[name] = measure_layer_list(model, args, S, N, flush, pk, params, params_read)
+            del model
+        out["sizes"].append(row)
+    out["clocks"] = sampler.stop()
+    out["gpu_launches"] = launch_count() - launches0
+    print(json.dumps(out))
+
+
 def run_katadra(args):
     from oracle import katadra_oracle as KO
     from llava.model import KatadraConfig, KatadraForCausalLM
@@ -1012,10 +1085,10 @@ def run_katadra(args):
 
 def main():
     args = parse_args()
-    if args.arch in ("katadra", "pefivik", "fezuzen"):
+    if args.arch in ("katadra", "pefivik", "fezuzen", "sofopel"):
         if not torch.cuda.is_available():
             raise RuntimeError(f"bench.py --arch {args.arch} needs a B200")
-        return {"katadra": run_katadra, "pefivik": run_pefivik, "fezuzen": run_fezuzen}[args.arch](args)
+        return {"katadra": run_katadra, "pefivik": run_pefivik, "fezuzen": run_fezuzen, "sofopel": run_sofopel}[args.arch](args)
     if args.impl == "reference":
         run_reference(args)
     else:

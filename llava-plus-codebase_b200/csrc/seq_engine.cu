@@ -160,8 +160,18 @@ int tc_min_rows() {  // fewest rows that take the tensor-core GEMM (below: the w
 struct Lin {  // one Linear call on the model's compute dtype
     const b2_model* m;
     cudaStream_t st;
+    // whether a product of these sizes takes the tensor-core GEMM (bf16 compute, a portion of a prompt)
+    bool tensor_cores(int N, int K, float* out, int64_t ldo, int M, const float* bias = nullptr, size_t w_row0 = 0, const void* bias16 = nullptr) const {
+        const SeqModel& s = *m->seq;
+        const int Np = (N + 7) / 8 * 8;
+        return s.d.compute == B2_COMPUTE_BF16 && M >= tc_min_rows() && N >= 32 && K % 8 == 0 && K >= 32 && K <= s.a16_w && ldo % 8 == 0 && Np <= ldo &&
+               (bias == nullptr || bias16 != nullptr) && (w_row0 == 0 || (N % 8 == 0 && (w_row0 * (size_t)K) % 8 == 0)) &&
+               (reinterpret_cast<uintptr_t>(out) & 15) == 0 && tc_enabled();
+    }
+    // a16_ready: A is already there as bf16 rows of pitch K in the model's a16 buffer (the producing kernel wrote them): no cast
     int operator()(const float* A, int64_t lda, const DevBuf& W, int N, int K, float* out, int64_t ldo, int M, int act = LIN_NONE,
-                   float alpha = 1.f, int accumulate = 0, const float* bias = nullptr, size_t w_row0 = 0, const void* bias16 = nullptr) const {
+                   float alpha = 1.f, int accumulate = 0, const float* bias = nullptr, size_t w_row0 = 0, const void* bias16 = nullptr,
+                   bool a16_ready = false) const {
         LinearArgs a;
         const SeqModel& s = *m->seq;
         a.A = A; a.lda = lda; a.ldw = K; a.w_dtype = s.w_dtype;
@@ -173,10 +183,8 @@ struct Lin {  // one Linear call on the model's compute dtype
         const int Np = (N + 7) / 8 * 8;
         // a block of rows inside a matrix (w_row0 > 0) has no zero rows behind it: then N itself must be a multiple of 8; a bias
         // rides the epilogue as bf16
-        if (a.round_a && M >= tc_min_rows() && N >= 32 && K % 8 == 0 && K >= 32 && K <= s.a16_w && ldo % 8 == 0 && Np <= ldo &&
-            (bias == nullptr || bias16 != nullptr) && (w_row0 == 0 || (N % 8 == 0 && (w_row0 * (size_t)K) % 8 == 0)) &&
-            (reinterpret_cast<uintptr_t>(out) & 15) == 0 && tc_enabled()) {
-            B2_TRY(cast_rows_bf16(A, lda, s.a16.p, K, M, K, st));
+        if (tensor_cores(N, K, out, ldo, M, bias, w_row0, bias16)) {
+            if (!a16_ready) B2_TRY(cast_rows_bf16(A, lda, s.a16.p, K, M, K, st));
             GemmArgs g;
             g.A = s.a16.p; g.lda = K; g.W = a.W; g.ldw = K; g.out = out; g.ld_out = (int)ldo; g.out_fp32 = 1; g.bias = bias16;
             g.M = M; g.N = Np; g.K = K; g.act = ACT_NONE; g.post = act; g.alpha = alpha; g.accumulate = accumulate;
@@ -466,10 +474,11 @@ static int seq_feed_forward(b2_model* m, const SeqLayerInfo& L, SeqWeights& W, c
         return lin(s.ffa.as<float>(), d.ff, W.down_w, width, d.ff, target, width, R, LIN_NONE, alpha, accumulate, W.down_b.as<float>(), 0, W.down_b16.p);
     }
     if (d.ff_kind == B2_FF_CLAMP_GLU) {
-        // [gate | up] in one matrix; the bounded gated unit a(g) (u + 1); a decode step takes product and unit in one launch
+        // [gate | up] in one matrix; the bounded gated unit a(g) (u + 1); a decode step of one row takes product and unit in one launch (more rows would
+        // stream the matrix once per row there)
         const int ff = d.ff, ffl = (2 * ff + 7) / 8 * 8;
         const GluAct act{d.ff_act_slope, d.ff_limit, 1.f};
-        if (R <= 8) {
+        if (R == 1) {
             GroupedLinearArgs gs;
             gs.A = h; gs.lda = width; gs.a_div = 1; gs.W = W.up_w.p; gs.ldw = width; gs.w_group_stride = 0; gs.w_dtype = s.w_dtype;
             gs.tile_group = s.zero_idx.as<int32_t>(); gs.tile_rows = 1; gs.out = s.ffa.as<float>(); gs.ld_out = ff;
@@ -478,6 +487,10 @@ static int seq_feed_forward(b2_model* m, const SeqLayerInfo& L, SeqWeights& W, c
             B2_TRY(linear_grouped_f32(gs, st));
         } else {
             B2_TRY(lin(h, width, W.up_w, 2 * ff, width, s.ff.as<float>(), ffl, R));
+            if (lin.tensor_cores(width, ff, target, width, R)) {   // the unit writes the bf16 rows that the second product reads
+                B2_TRY(glu_rows_f32(s.ff.as<float>(), ffl, nullptr, 0, R, ff, act, st, s.a16.p, ff));
+                return lin(nullptr, 0, W.down_w, width, ff, target, width, R, LIN_NONE, alpha, accumulate, nullptr, 0, nullptr, true);
+            }
             B2_TRY(glu_rows_f32(s.ff.as<float>(), ffl, s.ffa.as<float>(), ff, R, ff, act, st));
         }
         return lin(s.ffa.as<float>(), ff, W.down_w, width, ff, target, width, R, LIN_NONE, alpha, accumulate);

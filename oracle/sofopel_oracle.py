@@ -158,12 +158,12 @@ def diff_attention(h, p, mix, eps):
         js = [j for j in range(i + 1) if sees_chunk(i, j, size)]
         for a in range(H):
             g = a // (H // G)
-            maps = [softmax_attend(np.array([q[i, a, m] @ k[j, g, m] for j in js]) * scale, v[js, g], False) for m in range(2)]
+            maps = [softmax_attend(k[js, g, m] @ q[i, a, m] * scale, v[js, g], False) for m in range(2)]
             out[i, a] = rms_unit(maps[0] - lam * maps[1], eps) * (1.0 - d0)
     return out.reshape(T, H * dv) @ p["o"].T
 
 
-def window_attention(h, p, mix, eps):
+def window_attention(h, p, mix, eps, extra_one=True):
     H, G, dk, dv = int(mix["heads"]), int(mix["kv_heads"]), int(mix["dim"]), int(mix["vdim"])
     T = h.shape[0]
     q = rms_norm((h @ p["q"].T).reshape(T, H, dk), p["q.norm"], eps)
@@ -182,7 +182,7 @@ def window_attention(h, p, mix, eps):
         js = [j for j in range(i + 1) if sees_window(i, j, size, keep)]
         for a in range(H):
             g = a // (H // G)
-            out[i, a] = softmax_attend(np.array([q[i, a] @ k[j, g] for j in js]) * scale, v[js, g], True) * gate[i, a]
+            out[i, a] = softmax_attend(k[js, g] @ q[i, a] * scale, v[js, g], extra_one) * gate[i, a]
     return out.reshape(T, H * dv) @ p["o"].T
 
 
