@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
             const float sk = a.sink != nullptr ? a.sink[h] : a.sink_value, mf = fmaxf(m, sk), c0 = expf(m - mf);
             inv = c0 / fmaf(l, c0, expf(sk - mf));
         }
+        if (a.head_gate != nullptr) inv /= 1.f + expf(-a.head_gate[(size_t)r * a.ldg + h]);
 #pragma unroll
         for (int c = 0; c < AT_MAXC; ++c) {
             const int d = lane + 32 * c;
@@ -364,6 +365,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
                 const float sk = a.sink != nullptr ? a.sink[head] : a.sink_value, mf = fmaxf(m[i], sk), c0 = expf(m[i] - mf);
                 inv = c0 / fmaf(l[i], c0, expf(sk - mf));
             }
+            if (a.head_gate != nullptr) inv /= 1.f + expf(-a.head_gate[(size_t)row * a.ldg + head]);   // the head's sigmoid gate
 #pragma unroll
             for (int c = 0; c < MAXC; ++c) {
                 const int d = lane + 32 * c;
@@ -400,7 +402,7 @@ __global__ void __launch_bounds__(512) attn_merge_kernel(BiasAttnArgs a) {
             lsum = fmaf(ps[1], ws, lsum);
         }
         lsum = warp_sum(lsum);
-        if (lane == 0) inv_s = 1.f / lsum;
+        if (lane == 0) inv_s = a.head_gate != nullptr ? 1.f / (lsum * (1.f + expf(-a.head_gate[(size_t)r * a.ldg + h]))) : 1.f / lsum;
     }
     __syncthreads();
     const float inv = inv_s;

@@ -511,6 +511,7 @@ struct BiasAttnArgs {
     int mask_keep = 0;                            // MASK_WINDOW: positions j < mask_keep stay visible whatever their distance
     int Gv = 0;                                   // > 0: vcache holds Gv <= G value heads per slot and key head g reads value head g mod Gv
                                                   // (the maps of differential attention: G = maps * Gv key heads over one set of values)
+    const float* head_gate = nullptr; int64_t ldg = 0;   // non-null ([rows, ldg], entry h): a head's output is multiplied by sigmoid(head_gate[r, h])
     float* partial = nullptr; int nsplit = 1;     // split-KV scratch [rows*H*nsplit*(dv+2)] when nsplit > 1
     int tile_rows = 0;                            // consecutive rows that share a slot (a prompt portion: its rows; a decode step: 1);
                                                   // 0: one warp per (row, head) without shared key/value tiles

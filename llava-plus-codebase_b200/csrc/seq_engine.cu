@@ -381,10 +381,13 @@ static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& 
     if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
     aa.partial = state.attn_partial.as<float>();
     mask_of(d, aa);
+    const float* gates = proj + L.nq + L.nk + L.nv;
+    // one sigmoid per head rides in the attention's last write (unless the head's output is still to be joined or turned back)
+    const bool gate_in_attn = d.ga_gate == B2_GATE_HEAD && maps == 1 && !d.ga_rot_values;
+    if (gate_in_attn) { aa.head_gate = gates; aa.ldg = L.lproj_ld; }
     B2_TRY(attn_bias_f32(aa, st));
     const float* yo = s.y.as<float>();
     float* gated = s.gated.as<float>();
-    const float* gates = proj + L.nq + L.nk + L.nv;
     if (maps > 1) {   // a head's two maps: unit_rms(a1 - lambda a2) * (1 - diff)
         B2_TRY(diff_combine_f32(yo, (int64_t)maps * L.ng, gated, L.ng, R, H, dv, W.lambda, 1.f - d.ga_diff, s.d.norm_eps, st));
         yo = gated;
@@ -399,7 +402,7 @@ static int gqa_mixer(b2_model* m, b2_kv* kv, const SeqLayerInfo& L, SeqWeights& 
         B2_TRY(rotate_rows_f32(rb, st));
         yo = gated;
     }
-    if (d.ga_gate == B2_GATE_HEAD) {   // one sigmoid per head
+    if (d.ga_gate == B2_GATE_HEAD && !gate_in_attn) {   // one sigmoid per head
         B2_TRY(head_gate_f32(yo, L.ng, gates, L.lproj_ld, gated, L.ng, R, H, dv, st));
         yo = gated;
     }
